@@ -1,0 +1,151 @@
+"""tcgen05 GEMM kernels vs a plain PyTorch fp32 reference (single GPU)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(A, Bt):
+    return A.float() @ Bt.float().t()
+
+
+def _rel(out, ref):
+    return ((out.float() - ref).abs() / (ref.abs() + 1)).max().item()
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 320), (1024, 512, 1024), (2048, 2304, 512)])
+def test_plain_gemm_matches_fp32(native_lib, cta_group, shape):
+    from tileccl_b200.ops.gemm import GemmPlan
+    M, N, K = shape
+    torch.manual_seed(M + N + K)
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    plan = GemmPlan(A, Bt, cta_group=cta_group, timeout_ms=1000)
+    out = plan()
+    plan.check()
+    assert _rel(out, _ref(A, Bt)) < 1e-2
+    # a second call of the same plan gives the same bits
+    first = out.clone()
+    plan()
+    plan.check()
+    assert torch.equal(first, plan.out)
+
+
+def test_plain_gemm_strided_operands(native_lib):
+    from tileccl_b200.ops.gemm import GemmPlan
+    torch.manual_seed(3)
+    big_a = torch.randn(512, 1024, device="cuda", dtype=torch.bfloat16)
+    big_b = torch.randn(512, 1024, device="cuda", dtype=torch.bfloat16)
+    A, Bt = big_a[:, 256:768], big_b[:, :512]     # row pitch 1024, K = 512
+    out_big = torch.zeros(512, 1024, device="cuda", dtype=torch.bfloat16)
+    out = out_big[:, 512:]
+    plan = GemmPlan(A, Bt, out=out, cta_group=2, timeout_ms=1000)
+    plan()
+    plan.check()
+    assert _rel(out, _ref(A, Bt)) < 1e-2
+    assert out_big[:, :512].abs().max().item() == 0
+
+
+def test_plan_rejects_bad_shapes(native_lib):
+    from tileccl_b200.ops.gemm import GemmPlan
+    A = torch.randn(200, 64, device="cuda", dtype=torch.bfloat16)
+    Bt = torch.randn(256, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        GemmPlan(A, Bt, cta_group=1)
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_gemm_rs_world1_reduces_its_own_partials(native_lib, cta_group):
+    """World of one: the epilogue stages locally, the reduce warps wait on the
+    tile counters and produce the output - the whole fused path minus NVLink."""
+    from tileccl_b200.ops.gemm_rs import GemmRs
+    from tileccl_b200.parallel.heap import SymmetricHeap
+    torch.manual_seed(5)
+    M, N, K = 1024, 512, 384
+    heap = SymmetricHeap(64 << 20)
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    op = GemmRs(heap, A, Bt, cta_group=cta_group, timeout_ms=1000)
+    for _ in range(3):                      # epochs advance, counters are never reset
+        out = op()
+        op.check()
+        assert _rel(out, _ref(A, Bt)) < 1e-2
+        op.stage.fill_(float("nan"))        # stale staging must not leak into the next call
+    heap.close()
+
+
+def test_ag_gemm_world1(native_lib):
+    from tileccl_b200.ops.ag_gemm import AgGemm
+    from tileccl_b200.parallel.heap import SymmetricHeap
+    torch.manual_seed(6)
+    M, N, K = 512, 768, 256
+    heap = SymmetricHeap(64 << 20)
+    Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    op = AgGemm(heap, M, K, Bt, cta_group=2, timeout_ms=1000)
+    op.a_shard.copy_(torch.randn(M, K, device="cuda", dtype=torch.bfloat16))
+    out = op()
+    op.check()
+    assert _rel(out, _ref(op.a_full, Bt)) < 1e-2
+    heap.close()
+
+
+def test_wait_runs_out_and_reports_status(native_lib):
+    """A fused GEMM+RS whose counters can never reach the target (the plan is
+    told the world is 2 but only this rank ever signals) must come back with a
+    status word instead of hanging; the context stays usable."""
+    from tileccl_b200 import _native
+    from tileccl_b200.ops._plan import KernelTimeout, Plan
+    from tileccl_b200.parallel.heap import SymmetricHeap
+    heap = SymmetricHeap(64 << 20)
+    M, N, K = 512, 256, 64
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    stage = heap.empty((2, M // 2, N))
+    cnt = heap.zeros(((M // 2 // 128) * (N // 256),))
+    bar = heap.zeros((32,))
+    out = heap.empty((M // 2, N))
+    d = _native.GemmDesc()
+    d.mode, d.cta_group = _native.MODE_GEMM_RS, 1
+    d.M, d.N, d.K, d.lda, d.ldb, d.ldc = M, N, K, K, K, N
+    d.A, d.B = A.data_ptr(), Bt.data_ptr()
+    d.world, d.rank, d.seg_rows, d.comm_enabled = 2, 0, M // 2, 1
+    for s in range(2):                      # both "ranks" alias this GPU's buffers
+        d.dst_base[s] = stage.data_ptr()
+        d.dst_row_off[s] = 0
+        d.rs_tile_cnt[s] = cnt.data_ptr()
+        d.barrier[s] = bar.data_ptr()
+    d.rs_stage, d.rs_out, d.ld_out, d.rs_chunks = stage.data_ptr(), out.data_ptr(), N, 1
+    d.timeout_ns = 200_000_000              # 0.2 s
+    plan = Plan(d)
+    plan.run()
+    with pytest.raises(KernelTimeout) as ei:
+        plan.check()
+    assert ei.value.code in (5, 6)          # start barrier or tile counter
+    # the device still works
+    x = torch.ones(8, device="cuda")
+    assert float((x * 2).sum()) == 16.0
+    heap.close()
+
+
+def test_elementwise_kernels(native_lib):
+    from tileccl_b200.ops import elementwise as ew
+    torch.manual_seed(7)
+    gu = torch.randn(300, 512, device="cuda", dtype=torch.bfloat16)
+    out = ew.silu_mul(gu)
+    g, u = gu[:, :256].float(), gu[:, 256:].float()
+    ref = torch.nn.functional.silu(g) * u
+    assert ((out.float() - ref).abs() / (ref.abs() + 1)).max().item() < 1e-2
+
+    t = torch.empty(1 << 20, device="cuda", dtype=torch.bfloat16)
+    ew.fill_normal_(t, seed=1234)
+    t2 = torch.empty_like(t)
+    ew.fill_normal_(t2, seed=1234)
+    assert torch.equal(t, t2)
+    f = t.float()
+    assert abs(f.mean().item()) < 5e-3 and abs(f.std().item() - 1.0) < 1e-2
+
+    ref32 = torch.randn(5000, device="cuda")
+    got = (ref32 + 0.01).bfloat16()
+    want = ((got.float() - ref32).abs() / (ref32.abs() + 1)).max().item()
+    assert abs(ew.max_rel_err(got, ref32) - want) < 1e-6

@@ -1,0 +1,560 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: tcgen05.mma with the
+// accumulator in tensor memory (TMEM), operands staged in shared memory by
+// TMA, and three fused forms that share one mainloop:
+//
+//   kModePlain   D = A * B^T, D may live anywhere (local, a peer, or row
+//                segments scattered over peers: the epilogue-remote experiment)
+//   kModeGemmRs  GEMM -> reduce-scatter: the epilogue pushes bf16 partial tiles
+//                with 16-byte st.global into the staging slot of the rank that
+//                owns the rows, bumps that rank's per-tile counter with
+//                red.release.sys, and this rank's reduce warps sum the slots
+//                of its own segment as soon as a tile has all its partials
+//   kModeAgGemm  all-gather -> GEMM: gather warps pull the peers' A shards with
+//                16-byte P2P loads into the local gathered A and publish
+//                per-row-block counters; the TMA producer acquires a row
+//                block's counter before it loads tiles from it
+//
+// A is [M, K] row-major, B is [N, K] row-major (the "column-major B[K, N]" of
+// the reference), D is row-major.  fp32 accumulation, bf16 output.
+//
+// Warp roles (320 threads, one CTA per SM):
+//   warp 0      TMA producer (one lane)
+//   warp 1      TMEM allocation + tcgen05.mma issue (one lane, leader CTA only)
+//   warps 2-5   epilogue: tcgen05.ld -> bf16 -> swizzled smem transpose ->
+//               coalesced 16-byte global stores (local or peer)
+//   warps 6-9   communication: reduce warps (GEMM+RS) or gather warps (AG+GEMM)
+//
+// kCtaGroup = 2 pairs two CTAs (a 2x1 cluster) on one 256x256 tile: each CTA
+// loads its own 128 rows of A and its own 128 rows of B (no multicast), the
+// leader issues cta_group::2 MMAs that read both CTAs' shared memory, and each
+// CTA drains its own 128 accumulator rows.
+//
+// No TMA instruction here touches another GPU's memory: remote data moves by
+// plain ld/st only.  Every wait is bounded (deadline from %globaltimer); on
+// time-out the CTA records a status word, lets its copies land, frees its TMEM
+// and returns.
+//
+// Reference parity: comm_comp/gemm_sm90.cuh:48-140 (plain GEMM, TMA-store and
+// direct-store epilogues), comm_comp/rs_gemm_kernel_sm90.cuh:90-892 and
+// comm_comp/rs_dma_sm90.cuh:53-351 (fused GEMM+RS, which pulls peer tiles with
+// TMA and reduces in fp16 with red.global.add; here the partials are pushed
+// and summed in fp32), comm_comp/exp2_ag_gemm_granularity.cu:15-20 (the
+// in-kernel flag-gated all-gather GEMM that the reference describes but does
+// not implement).
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../ptx/ldst_sys.cuh"
+#include "../ptx/mbarrier.cuh"
+#include "../ptx/tcgen05.cuh"
+#include "../ptx/tma.cuh"
+#include "tile_sched.hpp"
+
+namespace tcl {
+
+enum GemmMode : int { kModePlain = 0, kModeGemmRs = 1, kModeAgGemm = 2 };
+
+constexpr int kMaxWorld = 8;
+
+// Status codes written to status[0] by the first role that gives up.
+enum GemmStatus : int {
+  kOk = 0,
+  kErrProducerEmpty = 1,   // TMA producer: stage never freed
+  kErrMmaFull = 2,         // MMA issuer: operands never landed
+  kErrMmaTmemEmpty = 3,    // MMA issuer: accumulator never drained
+  kErrEpiTmemFull = 4,     // epilogue: accumulator never completed
+  kErrStartBarrier = 5,    // a peer never arrived at the start barrier
+  kErrRsTileCount = 6,     // reduce warps: a tile never got all its partials
+  kErrAgFlag = 7,          // TMA producer: a gathered row block never arrived
+  kErrAgEndBarrier = 8     // a peer never finished reading this rank's shard
+};
+
+struct GemmParams {
+  int mode;
+  int M, N, K;
+  int ldc;        // output row pitch in elements
+  TileSched sched;
+  int world, rank;
+  int epoch;      // 1-based call number of the plan that owns the flag buffers
+  int comm_enabled;
+
+  // Output routing.  Rows are split in segments of seg_rows; row r of segment
+  // s goes to dst_base[s] + (dst_row_off[s] + r - s * seg_rows) * ldc.
+  int seg_rows;
+  __nv_bfloat16* dst_base[kMaxWorld];
+  long long dst_row_off[kMaxWorld];
+
+  // GEMM+RS
+  int* rs_tile_cnt[kMaxWorld];        // owner's counters, one per 128x256 tile of its segment
+  const __nv_bfloat16* rs_stage;      // this rank's staging [world][seg_rows][N]
+  __nv_bfloat16* rs_out;              // this rank's reduced shard [seg_rows][ld_out]
+  int ld_out;
+
+  // AG+GEMM
+  const __nv_bfloat16* ag_src[kMaxWorld];  // rank s's shard [seg_rows][K] (a peer pointer)
+  __nv_bfloat16* ag_full;                  // local gathered A [M][K]
+  int* ag_flags;                           // local counters, one per gather_rows row block
+  int gather_rows;
+  int* ag_done;                            // local: gather warps that finished (monotonic)
+  int* ag_read_done[kMaxWorld];            // rank s's "peers done reading me" counter
+
+  // Start barrier: rank s's arrival counter.
+  int* barrier[kMaxWorld];
+
+  int* status;                   // [4]: code, blockIdx, detail0, detail1
+  unsigned long long timeout_ns;
+};
+
+template <int kCtaGroup>
+struct GemmCfg {
+  static constexpr int BM = 128;                    // accumulator rows per CTA
+  static constexpr int TILE_M = BM * kCtaGroup;     // rows per scheduled tile
+  static constexpr int BN = 256;
+  static constexpr int BK = 64;                     // one 128-byte swizzle atom of bf16
+  static constexpr int UMMA_K = 16;
+  static constexpr int B_ROWS = BN / kCtaGroup;     // B rows each CTA loads
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (kCtaGroup == 1) ? 4 : 6;
+  static constexpr int EPI_WARPS = 4;
+  static constexpr int EPI_CHUNK_COLS = 64;         // bf16 columns per transpose chunk
+  static constexpr int EPI_BUF_BYTES = 32 * EPI_CHUNK_COLS * 2;   // 4 KiB
+  static constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES; // double buffered
+  static constexpr int COMM_WARPS = 4;
+  static constexpr int THREADS = (2 + EPI_WARPS + COMM_WARPS) * 32;
+  static constexpr int TMEM_COLS = 512;             // two accumulator buffers of BN columns
+  static constexpr int CTRL_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES + 1024;
+  static constexpr int GATHER_ITEM_ROWS = 8;
+};
+
+namespace detail {
+
+__device__ __forceinline__ void report(const GemmParams& p, volatile int* s_abort, int code, int d0,
+                                       int d1) {
+  if (atomicCAS(p.status, 0, code) == 0) {
+    p.status[1] = static_cast<int>(blockIdx.x);
+    p.status[2] = d0;
+    p.status[3] = d1;
+  }
+  *s_abort = 1;
+}
+
+}  // namespace detail
+
+template <int kCtaGroup>
+__global__ void __launch_bounds__(GemmCfg<kCtaGroup>::THREADS, 1)
+gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                  const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ GemmParams p) {
+  using Cfg = GemmCfg<kCtaGroup>;
+  using namespace ptx;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_u32 = smem_u32(smem_raw);
+  const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base_u32 - raw_u32);
+
+  const uint32_t stage_u32 = base_u32;
+  const uint32_t epi_u32 = base_u32 + Cfg::STAGES * Cfg::STAGE_BYTES;
+  uint8_t* ctrl = smem + Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES;
+  const uint32_t ctrl_u32 = epi_u32 + Cfg::EPI_BYTES;
+  // control block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | drain | tmem_ptr | abort | bcast
+  const uint32_t bar_full = ctrl_u32;
+  const uint32_t bar_empty = bar_full + 8 * Cfg::STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * Cfg::STAGES;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  const uint32_t bar_drain = bar_tempty + 16;
+  volatile uint32_t* s_tmem_ptr = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * Cfg::STAGES + 40);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(ctrl + 16 * Cfg::STAGES + 44);
+  volatile int* s_bcast = reinterpret_cast<volatile int*>(ctrl + 16 * Cfg::STAGES + 48);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (kCtaGroup == 2) ? cluster_ctarank() : 0u;
+  const int group_id = blockIdx.x / kCtaGroup;
+  const int num_groups = gridDim.x / kCtaGroup;
+  const unsigned long long deadline = globaltimer_ns() + p.timeout_ns;
+
+  const TileSched sched = p.sched;
+  const int num_tiles = sched.num_tiles();
+  const int k_blocks = (p.K + Cfg::BK - 1) / Cfg::BK;
+  const bool fused_comm = p.comm_enabled && p.world > 1;
+
+  // ---- set-up ---------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, Cfg::EPI_WARPS * kCtaGroup);
+    }
+    mbar_init(bar_drain, 1);
+    *s_abort = 0;
+    *s_bcast = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc<kCtaGroup>(smem_u32(const_cast<uint32_t*>(s_tmem_ptr)), Cfg::TMEM_COLS);
+    tmem_relinquish<kCtaGroup>();
+  }
+  // Start barrier, arrival side: one CTA tells every rank (itself included)
+  // that this rank has entered call `epoch`.
+  if (fused_comm && blockIdx.x == 0 && warp == 6 && lane < p.world) {
+    red_release_sys_add(p.barrier[lane], 1);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *s_tmem_ptr;
+  const int barrier_target = p.epoch * p.world;
+
+  // ---- roles ----------------------------------------------------------------
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int t = group_id; t < num_tiles && ok; t += num_groups) {
+        int m_blk, n_blk;
+        sched.tile(t, &m_blk, &n_blk);
+        const int m0 = m_blk * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BM;
+        const int n0 = n_blk * Cfg::BN + static_cast<int>(cta_rank) * Cfg::B_ROWS;
+        if (p.mode == kModeAgGemm && fused_comm && (m0 / p.seg_rows) != p.rank) {
+          // Rows [m0, m0+BM) lie in one gather block (gather_rows % BM == 0).
+          const int blk = m0 / p.gather_rows;
+          const int target = p.epoch * (p.gather_rows / Cfg::GATHER_ITEM_ROWS);
+          int seen = 0;
+          if (!wait_ge<false>(p.ag_flags + blk, target, s_abort, deadline, &seen)) {
+            detail::report(p, s_abort, kErrAgFlag, blk, seen);
+            ok = false;
+            break;
+          }
+          fence_proxy_async();
+        }
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t ph = (it / Cfg::STAGES) & 1;
+          if (!mbar_wait<kCtaGroup == 2>(bar_empty + 8 * s, ph ^ 1u, s_abort, deadline)) {
+            detail::report(p, s_abort, kErrProducerEmpty, t, kb);
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = stage_u32 + s * Cfg::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+          if constexpr (kCtaGroup == 1) {
+            mbar_arrive_expect_tx(bar_full + 8 * s, Cfg::STAGE_BYTES);
+            tma_load_2d(a_dst, &tmap_a, bar_full + 8 * s, kb * Cfg::BK, m0);
+            tma_load_2d(b_dst, &tmap_b, bar_full + 8 * s, kb * Cfg::BK, n0);
+          } else {
+            // Both CTAs' bytes are counted on the leader's barrier.
+            if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * Cfg::STAGE_BYTES);
+            const uint32_t lead_bar = mapa(bar_full + 8 * s, 0);
+            tma_load_2d_pair(a_dst, &tmap_a, lead_bar, kb * Cfg::BK, m0);
+            tma_load_2d_pair(b_dst, &tmap_b, lead_bar, kb * Cfg::BK, n0);
+          }
+        }
+      }
+      if (*s_abort) {
+        // Let this CTA's loads in flight land before shared memory goes away.
+        for (int i = 0; i < 64; ++i) __nanosleep(4000);
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer (leader CTA of the group) =====
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16_f32(Cfg::TILE_M, Cfg::BN);
+      int it = 0;
+      int lt = 0;
+      bool ok = true;
+      for (int t = group_id; t < num_tiles && ok; t += num_groups, ++lt) {
+        const int b = lt & 1;
+        if (!mbar_wait<kCtaGroup == 2>(bar_tempty + 8 * b, ((lt >> 1) & 1) ^ 1u, s_abort, deadline)) {
+          detail::report(p, s_abort, kErrMmaTmemEmpty, t, lt);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * Cfg::BN);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t ph = (it / Cfg::STAGES) & 1;
+          if (!mbar_wait(bar_full + 8 * s, ph, s_abort, deadline)) {
+            detail::report(p, s_abort, kErrMmaFull, t, kb);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_u32 = stage_u32 + s * Cfg::STAGE_BYTES;
+          const uint64_t a_desc = make_smem_desc_k_sw128(a_u32);
+          const uint64_t b_desc = make_smem_desc_k_sw128(a_u32 + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < Cfg::BK / Cfg::UMMA_K; ++k) {
+            mma_f16_ss<kCtaGroup>(d_tmem, advance_desc_k(a_desc, k * Cfg::UMMA_K * 2),
+                                  advance_desc_k(b_desc, k * Cfg::UMMA_K * 2), idesc,
+                                  (kb | k) != 0 ? 1u : 0u);
+          }
+          // Frees the stage (in both CTAs of a pair) once these MMAs have read it.
+          if constexpr (kCtaGroup == 1) tc_commit_1cta(bar_empty + 8 * s);
+          else tc_commit_2cta(bar_empty + 8 * s, 0x3);
+        }
+        if (!ok) break;
+        if constexpr (kCtaGroup == 1) tc_commit_1cta(bar_tfull + 8 * b);
+        else tc_commit_2cta(bar_tfull + 8 * b, 0x3);
+      }
+      if (*s_abort) {
+        // Wait (bounded) for the MMAs already issued before TMEM is freed.
+        if constexpr (kCtaGroup == 1) tc_commit_1cta(bar_drain);
+        else tc_commit_2cta(bar_drain, 0x1);
+        const unsigned long long d2 = globaltimer_ns() + 2000000ull;
+        for (int i = 0; i < (1 << 20); ++i) {
+          if (mbar_try_wait(bar_drain, 0) || globaltimer_ns() > d2) break;
+        }
+      }
+    }
+  } else if (warp < 2 + Cfg::EPI_WARPS) {
+    // ===== epilogue =====
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int ew = warp - 2;
+    const uint32_t my_buf = epi_u32 + ew * 2 * Cfg::EPI_BUF_BYTES;
+    bool ok = true;
+    bool barrier_passed = !(fused_comm && p.mode == kModeGemmRs);
+    int lt = 0;
+    for (int t = group_id; t < num_tiles && ok; t += num_groups, ++lt) {
+      int m_blk, n_blk;
+      sched.tile(t, &m_blk, &n_blk);
+      const int b = lt & 1;
+      const int row0 = m_blk * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BM;  // first row of this CTA's half
+      const int seg = row0 / p.seg_rows;
+      const int col0 = n_blk * Cfg::BN;
+      __nv_bfloat16* dst0 = p.dst_base[seg] +
+                            (p.dst_row_off[seg] + row0 - static_cast<long long>(seg) * p.seg_rows) * p.ldc +
+                            col0;
+
+      if (!barrier_passed) {
+        // Nobody may write a peer's staging before that peer has left the
+        // previous call: wait until every rank has arrived at this call.
+        int good = 1;
+        if (lane == 0) {
+          int seen = 0;
+          if (!wait_ge<true>(p.barrier[p.rank], barrier_target, s_abort, deadline, &seen)) {
+            detail::report(p, s_abort, kErrStartBarrier, barrier_target, seen);
+            good = 0;
+          }
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) { ok = false; break; }
+        barrier_passed = true;
+      }
+
+      int good = 1;
+      if (lane == 0) {
+        if (!mbar_wait<kCtaGroup == 2>(bar_tfull + 8 * b, (lt >> 1) & 1, s_abort, deadline)) {
+          detail::report(p, s_abort, kErrEpiTmemFull, t, lt);
+          good = 0;
+        }
+      }
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) { ok = false; break; }
+      tc_fence_after_sync();
+
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                             static_cast<uint32_t>(b * Cfg::BN);
+#pragma unroll 1
+      for (int c = 0; c < Cfg::BN / Cfg::EPI_CHUNK_COLS; ++c) {
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32b_x32(t_row + c * Cfg::EPI_CHUNK_COLS, v0);
+        tmem_ld_32x32b_x32(t_row + c * Cfg::EPI_CHUNK_COLS + 32, v1);
+        tmem_ld_wait();
+        if (c == Cfg::BN / Cfg::EPI_CHUNK_COLS - 1) {
+          // Last read of this accumulator buffer: hand it back to the MMA issuer.
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kCtaGroup == 1) mbar_arrive(bar_tempty + 8 * b);
+            else mbar_arrive_cluster(mapa(bar_tempty + 8 * b, 0));
+          }
+        }
+        // Row `lane` of this warp's 32 rows, 64 columns -> 8 chunks of 16 bytes,
+        // chunk j stored at slot j ^ (lane & 7) so that both the row-wise
+        // writes and the transposed reads are bank-conflict free.
+        const uint32_t buf = my_buf + (c & 1) * Cfg::EPI_BUF_BYTES;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 w;
+          w.x = pack_bf16x2(v0[8 * j + 0], v0[8 * j + 1]);
+          w.y = pack_bf16x2(v0[8 * j + 2], v0[8 * j + 3]);
+          w.z = pack_bf16x2(v0[8 * j + 4], v0[8 * j + 5]);
+          w.w = pack_bf16x2(v0[8 * j + 6], v0[8 * j + 7]);
+          sts_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), w);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 w;
+          w.x = pack_bf16x2(v1[8 * j + 0], v1[8 * j + 1]);
+          w.y = pack_bf16x2(v1[8 * j + 2], v1[8 * j + 3]);
+          w.z = pack_bf16x2(v1[8 * j + 4], v1[8 * j + 5]);
+          w.w = pack_bf16x2(v1[8 * j + 6], v1[8 * j + 7]);
+          sts_v4(buf + lane * 128 + (((j + 4) ^ (lane & 7)) << 4), w);
+        }
+        __syncwarp();
+        // 8 lanes cover one row's 128 contiguous bytes; 4 rows per instruction.
+        const int ch = lane & 7;
+        const int gcol = col0 + c * Cfg::EPI_CHUNK_COLS + ch * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + (lane >> 3);
+          const uint4 w = lds_v4(buf + r * 128 + ((ch ^ (r & 7)) << 4));
+          const int grow = row0 + q * 32 + r;
+          if (grow < p.M && gcol < p.N) {
+            st_v4(dst0 + static_cast<long long>(q * 32 + r) * p.ldc + c * Cfg::EPI_CHUNK_COLS + ch * 8, w);
+          }
+        }
+      }
+      if (p.mode == kModeGemmRs && p.comm_enabled) {
+        // This warp's 32 rows of the tile are stored: one release at system
+        // scope publishes them to the owner.  Each of the four epilogue warps
+        // signals on its own (a tile is complete at world * 4 arrivals), so no
+        // CTA-wide barrier sits on the store path.
+        __syncwarp();
+        if (lane == 0) {
+          const int seg_row = (row0 - seg * p.seg_rows) / Cfg::BM;
+          red_release_sys_add(p.rs_tile_cnt[seg] + seg_row * sched.n_tiles + n_blk, 1);
+        }
+      }
+    }
+  } else {
+    // ===== communication warps =====
+    const int cw = warp - (2 + Cfg::EPI_WARPS);
+    const int ctid = threadIdx.x - (2 + Cfg::EPI_WARPS) * 32;  // 0..127
+    if (p.mode == kModeGemmRs && p.comm_enabled) {
+      // ---- reduce warps: sum the `world` staged partials of each tile of this
+      // rank's segment, in the order in which the producers complete them ----
+      const int items = (p.seg_rows / Cfg::BM) * sched.n_tiles;
+      const int target = p.epoch * p.world * Cfg::EPI_WARPS;
+      const size_t slot_elems = static_cast<size_t>(p.seg_rows) * p.N;
+      for (int j = blockIdx.x; j < items; j += gridDim.x) {
+        if (ctid == 0) {
+          int seen = 0;
+          if (!wait_ge<true>(p.rs_tile_cnt[p.rank] + j, target, s_abort, deadline, &seen, 256)) {
+            detail::report(p, s_abort, kErrRsTileCount, j, seen);
+            *s_bcast = 1;
+          }
+        }
+        named_bar_sync(2, Cfg::COMM_WARPS * 32);
+        if (*s_bcast) break;
+        const int seg_row = j / sched.n_tiles;
+        const int n_blk = j - seg_row * sched.n_tiles;
+        const int colc = ctid & 31;  // 16-byte column chunk of the 256-column tile
+        const size_t tile_off = static_cast<size_t>(seg_row) * Cfg::BM * p.N + n_blk * Cfg::BN + colc * 8;
+#pragma unroll 2
+        for (int pass = 0; pass < Cfg::BM / 4; ++pass) {
+          const int r = pass * 4 + (ctid >> 5);
+          float acc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+          for (int src = 0; src < p.world; ++src) {
+            const uint4 w = ld_v4_stream(p.rs_stage + src * slot_elems + tile_off + static_cast<size_t>(r) * p.N);
+            const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              acc[2 * e] += __uint_as_float(u[e] << 16);
+              acc[2 * e + 1] += __uint_as_float(u[e] & 0xffff0000u);
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16x2(__float_as_uint(acc[0]), __float_as_uint(acc[1]));
+          o.y = pack_bf16x2(__float_as_uint(acc[2]), __float_as_uint(acc[3]));
+          o.z = pack_bf16x2(__float_as_uint(acc[4]), __float_as_uint(acc[5]));
+          o.w = pack_bf16x2(__float_as_uint(acc[6]), __float_as_uint(acc[7]));
+          st_v4(p.rs_out + (static_cast<size_t>(seg_row) * Cfg::BM + r) * p.ld_out + n_blk * Cfg::BN + colc * 8, o);
+        }
+      }
+    } else if (p.mode == kModeAgGemm && fused_comm) {
+      // ---- gather warps: pull the peers' shards into the local gathered A ----
+      int good = 1;
+      if (lane == 0) {
+        int seen = 0;
+        if (!wait_ge<true>(p.barrier[p.rank], barrier_target, s_abort, deadline, &seen)) {
+          detail::report(p, s_abort, kErrStartBarrier, barrier_target, seen);
+          good = 0;
+        }
+      }
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (good) {
+        const int items_per_seg = p.seg_rows / Cfg::GATHER_ITEM_ROWS;
+        const int total = (p.world - 1) * items_per_seg;
+        const int gw = blockIdx.x * Cfg::COMM_WARPS + cw;
+        const int n_gw = gridDim.x * Cfg::COMM_WARPS;
+        const size_t item_bytes = static_cast<size_t>(Cfg::GATHER_ITEM_ROWS) * p.K * 2;
+        for (int j = gw; j < total; j += n_gw) {
+          const int step = j / items_per_seg + 1;
+          const int i = j - (step - 1) * items_per_seg;
+          const int seg = (p.rank + step) % p.world;
+          const size_t row_in_seg = static_cast<size_t>(i) * Cfg::GATHER_ITEM_ROWS;
+          const char* src = reinterpret_cast<const char*>(p.ag_src[seg] + row_in_seg * p.K);
+          const size_t grow = static_cast<size_t>(seg) * p.seg_rows + row_in_seg;
+          char* dst = reinterpret_cast<char*>(p.ag_full + grow * p.K);
+          constexpr int kUnroll = 8;
+          size_t off = static_cast<size_t>(lane) * 16;
+          for (; off + (kUnroll - 1) * 512 < item_bytes; off += kUnroll * 512) {
+            uint4 w[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) w[u] = ld_v4_stream(src + off + u * 512);
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) st_v4(dst + off + u * 512, w[u]);
+          }
+          for (; off < item_bytes; off += 512) st_v4(dst + off, ld_v4_stream(src + off));
+          // The consumer of these rows is TMA (async proxy) on another SM.
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) red_release_gpu_add(p.ag_flags + static_cast<int>(grow / p.gather_rows), 1);
+        }
+        // Tell the peers when this rank has read everything it needs from them:
+        // the last gather warp of the grid sends one signal per peer.
+        if (lane == 0) {
+          const int done = atom_add_acq_rel_gpu(p.ag_done, 1) + 1;
+          if (done == p.epoch * n_gw) {
+            for (int s = 0; s < p.world; ++s)
+              if (s != p.rank) red_release_sys_add(p.ag_read_done[s], 1);
+          }
+        }
+        // One warp keeps the kernel alive until every peer has finished reading
+        // this rank's shard, so the caller may overwrite it after the kernel.
+        if (blockIdx.x == 0 && cw == 0 && lane == 0) {
+          int seen = 0;
+          if (!wait_ge<true>(p.ag_read_done[p.rank], p.epoch * (p.world - 1), s_abort, deadline, &seen, 512)) {
+            detail::report(p, s_abort, kErrAgEndBarrier, p.epoch * (p.world - 1), seen);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- tear-down ------------------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) {
+    // The peer CTA may still be read by the leader's MMAs or signal our barriers.
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc<kCtaGroup>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace tcl

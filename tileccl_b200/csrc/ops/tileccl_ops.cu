@@ -1,0 +1,393 @@
+// Host side of libtileccl.so: plan construction / validation / launch for the
+// sm_100a GEMM family, and the small stand-alone kernels (device barrier,
+// SiLU*mul, N(0,1) fill, verify).  See tileccl_ops.h for the contract.
+#include "tileccl_ops.h"
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "../gemm/gemm_sm100.cuh"
+
+namespace {
+
+using namespace tcl;
+
+struct GemmPlan {
+  CUtensorMap tmap_a;
+  CUtensorMap tmap_b;
+  GemmParams params;
+  int cta_group;
+  int grid;
+};
+
+void set_err(char* err, int errlen, const char* msg) {
+  if (err && errlen > 0) {
+    std::snprintf(err, static_cast<size_t>(errlen), "%s", msg);
+  }
+}
+
+template <int G>
+cudaError_t launch_gemm(const GemmPlan* pl, cudaStream_t stream) {
+  using Cfg = GemmCfg<G>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<G>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(pl->grid), 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = G;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<G>, pl->tmap_a, pl->tmap_b, pl->params);
+}
+
+// ---------------------------------------------------------------------------
+// Device barrier (stand-alone form of the barrier built into the fused kernels)
+// ---------------------------------------------------------------------------
+struct BarrierArgs {
+  int* counters[kMaxWorld];
+};
+
+__global__ void barrier_all_kernel(BarrierArgs a, int world, int rank, int epoch, int* status,
+                                   unsigned long long timeout_ns) {
+  const int lane = threadIdx.x;
+  if (lane < world) ptx::red_release_sys_add(a.counters[lane], 1);
+  if (lane == 0) {
+    const unsigned long long deadline = ptx::globaltimer_ns() + timeout_ns;
+    int seen = 0;
+    if (!ptx::wait_ge<true>(a.counters[rank], epoch * world, nullptr, deadline, &seen)) {
+      if (atomicCAS(status, 0, kErrStartBarrier) == 0) {
+        status[1] = rank;
+        status[2] = epoch * world;
+        status[3] = seen;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// SiLU(gate) * up
+// ---------------------------------------------------------------------------
+__global__ void silu_mul_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, long long rows,
+                                long long ffn8) {
+  // One thread per 8 output elements; a row of gu holds 2*ffn8 chunks.
+  const long long total = rows * ffn8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / ffn8;
+    const long long c = i - r * ffn8;
+    const uint4 g = gu[r * 2 * ffn8 + c];
+    const uint4 u = gu[r * 2 * ffn8 + ffn8 + c];
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+    const uint32_t uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float g0 = __uint_as_float(gw[e] << 16), g1 = __uint_as_float(gw[e] & 0xffff0000u);
+      const float u0 = __uint_as_float(uw[e] << 16), u1 = __uint_as_float(uw[e] & 0xffff0000u);
+      const float o0 = g0 / (1.f + __expf(-g0)) * u0;
+      const float o1 = g1 / (1.f + __expf(-g1)) * u1;
+      ow[e] = ptx::pack_bf16x2(__float_as_uint(o0), __float_as_uint(o1));
+    }
+    out[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// N(mean, std) bf16 fill: counter-based hash -> two uniforms -> Box-Muller.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+__global__ void fill_normal_bf16_kernel(__nv_bfloat16* dst, long long n, uint64_t seed, float mean,
+                                        float stdv) {
+  // Each thread produces a pair (2i, 2i+1) from one hash value.
+  const long long pairs = (n + 1) / 2;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < pairs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint64_t h = mix64(seed * 0xD1342543DE82EF95ull + static_cast<uint64_t>(i));
+    const float u1 = (static_cast<float>(static_cast<uint32_t>(h >> 40)) + 1.0f) * (1.0f / 16777217.0f);
+    const float u2 = static_cast<float>(static_cast<uint32_t>(h) >> 8) * (1.0f / 16777216.0f);
+    const float rad = sqrtf(-2.0f * __logf(u1));
+    float s, c;
+    __sincosf(6.283185307179586f * u2, &s, &c);
+    dst[2 * i] = __float2bfloat16_rn(mean + stdv * rad * c);
+    if (2 * i + 1 < n) dst[2 * i + 1] = __float2bfloat16_rn(mean + stdv * rad * s);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Verify: max |got - ref| / (|ref| + 1).  Two passes through a scratch array
+// of per-block maxima.
+// ---------------------------------------------------------------------------
+constexpr int kVerifyBlocks = 1024;
+
+__global__ void max_rel_err_partial(const __nv_bfloat16* got, const float* ref, long long n,
+                                    float* scratch) {
+  float m = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float r = ref[i];
+    const float g = __bfloat162float(got[i]);
+    float e = fabsf(g - r) / (fabsf(r) + 1.f);
+    if (!(e == e)) e = 3.4e38f;  // NaN counts as the worst error
+    m = fmaxf(m, e);
+  }
+  __shared__ float sm[256];
+  sm[threadIdx.x] = m;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) sm[threadIdx.x] = fmaxf(sm[threadIdx.x], sm[threadIdx.x + s]);
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) scratch[blockIdx.x] = sm[0];
+}
+
+__global__ void max_rel_err_final(const float* scratch, int nblocks, float* result) {
+  __shared__ float sm[256];
+  float m = 0.f;
+  for (int i = threadIdx.x; i < nblocks; i += blockDim.x) m = fmaxf(m, scratch[i]);
+  sm[threadIdx.x] = m;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) sm[threadIdx.x] = fmaxf(sm[threadIdx.x], sm[threadIdx.x + s]);
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) result[0] = sm[0];
+}
+
+}  // namespace
+
+extern "C" {
+
+int tcl_gemm_smem_bytes(int cta_group) {
+  return cta_group == 2 ? GemmCfg<2>::SMEM_BYTES : GemmCfg<1>::SMEM_BYTES;
+}
+
+void tcl_sched_tile(int m_tiles, int n_tiles, int group_m, int order, int world, int rank,
+                    int rs_chunks, int t, int* m_blk, int* n_blk) {
+  TileSched s{m_tiles, n_tiles, group_m, order, world, rank, rs_chunks};
+  s.tile(t, m_blk, n_blk);
+}
+
+void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
+  const int G = d->cta_group;
+  if (G != 1 && G != 2) { set_err(err, errlen, "cta_group must be 1 or 2"); return nullptr; }
+  const int tile_m = 128 * G;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) { set_err(err, errlen, "M, N, K must be positive"); return nullptr; }
+  if (d->M % tile_m != 0) { set_err(err, errlen, "M must be a multiple of 128 * cta_group"); return nullptr; }
+  if (d->N % 256 != 0) { set_err(err, errlen, "N must be a multiple of 256"); return nullptr; }
+  if (d->K % 8 != 0 || d->lda % 8 != 0 || d->ldb % 8 != 0 || d->ldc % 8 != 0) {
+    set_err(err, errlen, "K and the row pitches must be multiples of 8 elements (16 bytes)");
+    return nullptr;
+  }
+  if ((reinterpret_cast<uintptr_t>(d->A) & 15) || (reinterpret_cast<uintptr_t>(d->B) & 15)) {
+    set_err(err, errlen, "A and B must be 16-byte aligned");
+    return nullptr;
+  }
+  if (d->world < 1 || d->world > TCL_MAX_WORLD || d->rank < 0 || d->rank >= d->world) {
+    set_err(err, errlen, "world must be 1..8 and rank inside it");
+    return nullptr;
+  }
+  if (d->seg_rows <= 0 || d->seg_rows % tile_m != 0 || d->M % d->seg_rows != 0 ||
+      d->M / d->seg_rows > TCL_MAX_WORLD) {
+    set_err(err, errlen, "seg_rows must divide M into at most 8 segments of whole tiles");
+    return nullptr;
+  }
+  const int nseg = d->M / d->seg_rows;
+  for (int s = 0; s < nseg; ++s) {
+    if (!d->dst_base[s] || (reinterpret_cast<uintptr_t>(d->dst_base[s]) & 15)) {
+      set_err(err, errlen, "every dst_base must be set and 16-byte aligned");
+      return nullptr;
+    }
+  }
+  if (!d->status) { set_err(err, errlen, "status buffer missing"); return nullptr; }
+
+  GemmPlan* pl = new (std::nothrow) GemmPlan();
+  if (!pl) { set_err(err, errlen, "out of host memory"); return nullptr; }
+  std::memset(pl, 0, sizeof(*pl));
+  GemmParams& p = pl->params;
+  p.mode = d->mode;
+  p.M = d->M; p.N = d->N; p.K = d->K; p.ldc = d->ldc;
+  p.world = d->world; p.rank = d->rank;
+  p.comm_enabled = d->comm_enabled;
+  p.seg_rows = d->seg_rows;
+  for (int s = 0; s < TCL_MAX_WORLD; ++s) {
+    p.dst_base[s] = static_cast<__nv_bfloat16*>(d->dst_base[s]);
+    p.dst_row_off[s] = d->dst_row_off[s];
+    p.rs_tile_cnt[s] = d->rs_tile_cnt[s];
+    p.ag_src[s] = static_cast<const __nv_bfloat16*>(d->ag_src[s]);
+    p.ag_read_done[s] = d->ag_read_done[s];
+    p.barrier[s] = d->barrier[s];
+  }
+  p.status = d->status;
+  p.timeout_ns = d->timeout_ns ? d->timeout_ns : 4000000000ull;
+
+  TileSched& sc = p.sched;
+  sc.m_tiles = d->M / tile_m;
+  sc.n_tiles = d->N / 256;
+  sc.world = 1; sc.rank = 0; sc.rs_chunks = 1; sc.order = kOrderPlain;
+  sc.group_m = d->group_m > 0 ? d->group_m : (G == 2 ? 8 : 16);
+
+  auto fail = [&](const char* m) -> void* { set_err(err, errlen, m); delete pl; return nullptr; };
+
+  if (d->mode == TCL_MODE_GEMM_RS) {
+    if (nseg != d->world) return fail("GEMM+RS: M / seg_rows must equal world");
+    if (d->ldc != d->N) return fail("GEMM+RS: staging pitch (ldc) must equal N");
+    sc.order = kOrderRsPush; sc.world = d->world; sc.rank = d->rank;
+    const int st = sc.m_tiles / d->world;
+    int g = d->rs_chunks > 0 ? d->rs_chunks : 1;
+    if (st % g != 0) return fail("GEMM+RS: rs_chunks must divide the tile rows of a segment");
+    sc.rs_chunks = g;
+    if (d->group_m <= 0) {
+      const int cpr = st / g;
+      sc.group_m = cpr < sc.group_m ? cpr : sc.group_m;
+    }
+    if (d->comm_enabled) {
+      if (!d->rs_stage || !d->rs_out || d->ld_out % 8 != 0 || d->ld_out < d->N)
+        return fail("GEMM+RS: rs_stage / rs_out / ld_out invalid");
+      for (int s = 0; s < d->world; ++s) {
+        if (!d->rs_tile_cnt[s]) return fail("GEMM+RS: rs_tile_cnt missing for a rank");
+        if (d->world > 1 && !d->barrier[s]) return fail("GEMM+RS: barrier counter missing for a rank");
+      }
+    }
+    p.rs_stage = static_cast<const __nv_bfloat16*>(d->rs_stage);
+    p.rs_out = static_cast<__nv_bfloat16*>(d->rs_out);
+    p.ld_out = d->ld_out;
+  } else if (d->mode == TCL_MODE_AG_GEMM) {
+    if (nseg != d->world) return fail("AG+GEMM: M / seg_rows must equal world");
+    if (d->lda != d->K) return fail("AG+GEMM: gathered A must be dense (lda == K)");
+    sc.order = kOrderAgPull; sc.world = d->world; sc.rank = d->rank;
+    if (d->comm_enabled && d->world > 1) {
+      if (d->gather_rows < 128 || d->gather_rows % tile_m != 0 && d->gather_rows % 128 != 0)
+        return fail("AG+GEMM: gather_rows must be a multiple of 128");
+      if (d->gather_rows % 128 != 0 || d->seg_rows % d->gather_rows != 0)
+        return fail("AG+GEMM: gather_rows must be a multiple of 128 that divides seg_rows");
+      if (!d->ag_flags || !d->ag_done) return fail("AG+GEMM: flag buffers missing");
+      for (int s = 0; s < d->world; ++s) {
+        if (!d->ag_src[s] || !d->ag_read_done[s] || !d->barrier[s])
+          return fail("AG+GEMM: peer pointers missing for a rank");
+        if (reinterpret_cast<uintptr_t>(d->ag_src[s]) & 15) return fail("AG+GEMM: ag_src must be 16-byte aligned");
+      }
+    }
+    p.ag_full = static_cast<__nv_bfloat16*>(const_cast<void*>(d->A));
+    p.ag_flags = d->ag_flags;
+    p.gather_rows = d->gather_rows > 0 ? d->gather_rows : d->seg_rows;
+    p.ag_done = d->ag_done;
+  } else if (d->mode != TCL_MODE_PLAIN) {
+    return fail("unknown mode");
+  } else {
+    p.comm_enabled = 0;
+  }
+
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    return fail("no CUDA device");
+  int grid = d->num_ctas > 0 ? d->num_ctas : sms;
+  if (grid > sms) grid = sms;
+  const int max_useful = sc.num_tiles() * G;
+  if (grid > max_useful && d->mode == TCL_MODE_PLAIN) grid = max_useful;
+  grid -= grid % G;
+  if (grid < G) return fail("grid too small");
+  pl->grid = grid;
+  pl->cta_group = G;
+
+  const int box_b = 256 / G;
+  int r = ptx::encode_tmap_bf16_k64(&pl->tmap_a, d->A, static_cast<uint64_t>(d->M),
+                                    static_cast<uint64_t>(d->K), static_cast<uint64_t>(d->lda), 128);
+  if (r != 0) return fail("cuTensorMapEncodeTiled failed for A");
+  r = ptx::encode_tmap_bf16_k64(&pl->tmap_b, d->B, static_cast<uint64_t>(d->N),
+                                static_cast<uint64_t>(d->K), static_cast<uint64_t>(d->ldb),
+                                static_cast<uint32_t>(box_b));
+  if (r != 0) return fail("cuTensorMapEncodeTiled failed for B");
+  return pl;
+}
+
+int tcl_gemm_plan_run(void* plan, int epoch, void* stream) {
+  GemmPlan* pl = static_cast<GemmPlan*>(plan);
+  if (!pl) return static_cast<int>(cudaErrorInvalidValue);
+  pl->params.epoch = epoch;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = pl->cta_group == 2 ? launch_gemm<2>(pl, st) : launch_gemm<1>(pl, st);
+  return static_cast<int>(e);
+}
+
+void tcl_gemm_plan_destroy(void* plan) { delete static_cast<GemmPlan*>(plan); }
+int tcl_gemm_plan_grid(void* plan) { return plan ? static_cast<GemmPlan*>(plan)->grid : 0; }
+int tcl_gemm_plan_launches(void* plan) { return plan ? 1 : 0; }
+
+int tcl_barrier_all(int32_t* const* counters, int world, int rank, int epoch, int32_t* status,
+                    uint64_t timeout_ns, void* stream) {
+  if (world < 1 || world > TCL_MAX_WORLD || rank < 0 || rank >= world) return static_cast<int>(cudaErrorInvalidValue);
+  BarrierArgs a = {};
+  for (int i = 0; i < world; ++i) a.counters[i] = counters[i];
+  barrier_all_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      a, world, rank, epoch, status, timeout_ns ? timeout_ns : 4000000000ull);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int tcl_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t ffn, void* stream) {
+  if (ffn % 8 != 0 || rows <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  const long long total = rows * (ffn / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  silu_mul_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(gate_up), static_cast<uint4*>(out), rows, ffn / 8);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int tcl_fill_normal_bf16(void* dst, int64_t n, uint64_t seed, float mean, float stdv, void* stream) {
+  if (n <= 0) return 0;
+  long long blocks = ((n + 1) / 2 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  fill_normal_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(dst), n, seed, mean, stdv);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int tcl_max_rel_err(const void* got_bf16, const float* ref, int64_t n, float* scratch, float* result,
+                    void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  long long blocks = (n + 255) / 256;
+  if (blocks > kVerifyBlocks) blocks = kVerifyBlocks;
+  if (blocks < 1) blocks = 1;
+  max_rel_err_partial<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(got_bf16), ref, n, scratch);
+  max_rel_err_final<<<1, 256, 0, st>>>(scratch, static_cast<int>(blocks), result);
+  return static_cast<int>(cudaGetLastError());
+}
+
+const char* tcl_status_string(int code) {
+  switch (code) {
+    case kOk: return "ok";
+    case kErrProducerEmpty: return "TMA producer timed out waiting for a free stage";
+    case kErrMmaFull: return "MMA issuer timed out waiting for operands";
+    case kErrMmaTmemEmpty: return "MMA issuer timed out waiting for a drained accumulator";
+    case kErrEpiTmemFull: return "epilogue timed out waiting for an accumulator";
+    case kErrStartBarrier: return "a peer never arrived at the start barrier";
+    case kErrRsTileCount: return "reduce warps timed out waiting for a tile's partials";
+    case kErrAgFlag: return "TMA producer timed out waiting for a gathered row block";
+    case kErrAgEndBarrier: return "a peer never finished reading this rank's shard";
+    default: return "unknown status";
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,90 @@
+/* C interface of libtileccl.so: GEMM plans (plain, fused GEMM->reduce-scatter,
+ * fused all-gather->GEMM), the device barrier, the fused SiLU*mul, fill and
+ * verify kernels.  Everything takes raw device pointers and a CUDA stream so
+ * that Python (ctypes), the C++ benchmarks and other runtimes can call it.
+ *
+ * Reference parity: the init-once / run-many GEMM wrapper
+ * (comm_comp/gemm_sm90.cuh:99-140), the fused kernel's arguments
+ * (comm_comp/rs_dma_sm90.cuh:93-126), barrier_all_on_stream
+ * (comm_comp/ipc_multiproc.cuh:184-201), verify_kernel
+ * (comm_comp/exp3_gemm_rs_fused.cu:252-270), fill_half
+ * (comm_comp/common.cuh:190-223).
+ */
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TCL_MAX_WORLD 8
+
+enum { TCL_MODE_PLAIN = 0, TCL_MODE_GEMM_RS = 1, TCL_MODE_AG_GEMM = 2 };
+
+typedef struct tcl_gemm_desc {
+  int32_t mode;         /* TCL_MODE_* */
+  int32_t cta_group;    /* 1: one CTA per 128x256 tile; 2: CTA pair per 256x256 tile */
+  int32_t M, N, K;      /* A is [M,K] (gathered size for AG), B is [N,K], D is [M,N] */
+  int32_t lda, ldb, ldc;/* row pitches in elements */
+  const void* A;        /* local; for TCL_MODE_AG_GEMM the gathered buffer ag_full */
+  const void* B;
+  int32_t world, rank;
+  int32_t seg_rows;     /* rows per output segment (M for a single segment) */
+  int32_t comm_enabled; /* 0: same schedule, no peer traffic, no flags (the "ctrl" variant) */
+  void* dst_base[TCL_MAX_WORLD];
+  int64_t dst_row_off[TCL_MAX_WORLD];
+  /* GEMM+RS */
+  int32_t* rs_tile_cnt[TCL_MAX_WORLD];
+  const void* rs_stage;
+  void* rs_out;
+  int32_t ld_out;
+  int32_t rs_chunks;
+  /* AG+GEMM */
+  const void* ag_src[TCL_MAX_WORLD];
+  int32_t* ag_flags;
+  int32_t gather_rows;
+  int32_t* ag_done;
+  int32_t* ag_read_done[TCL_MAX_WORLD];
+  /* common */
+  int32_t* barrier[TCL_MAX_WORLD];
+  int32_t* status;      /* 4 ints, zeroed by the caller */
+  uint64_t timeout_ns;  /* bound of every device-side wait; 0 = 4 s */
+  int32_t group_m;      /* raster group height; 0 = default */
+  int32_t num_ctas;     /* 0 = one per SM */
+} tcl_gemm_desc;
+
+/* Returns NULL and fills err on invalid arguments. */
+void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen);
+/* Launches one call; epoch is the 1-based call number shared by all ranks. */
+int tcl_gemm_plan_run(void* plan, int epoch, void* stream);
+void tcl_gemm_plan_destroy(void* plan);
+int tcl_gemm_plan_grid(void* plan);
+int tcl_gemm_smem_bytes(int cta_group);
+/* Number of kernels one run launches (for launch accounting). */
+int tcl_gemm_plan_launches(void* plan);
+
+/* Schedule, exposed for host-side tests: tile t -> (m_blk, n_blk). */
+void tcl_sched_tile(int m_tiles, int n_tiles, int group_m, int order, int world, int rank,
+                    int rs_chunks, int t, int* m_blk, int* n_blk);
+
+/* Device barrier over `world` ranks: every rank adds 1 to every rank's counter
+ * and waits until its own reaches epoch * world.  status[0] != 0 on time-out. */
+int tcl_barrier_all(int32_t* const* counters, int world, int rank, int epoch, int32_t* status,
+                    uint64_t timeout_ns, void* stream);
+
+/* out[r, c] = silu(gu[r, c]) * gu[r, ffn + c]; gu is [rows, 2*ffn] bf16. */
+int tcl_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t ffn, void* stream);
+
+/* N(mean, std) bf16 fill, counter-based (same seed+offset => same values). */
+int tcl_fill_normal_bf16(void* dst, int64_t n, uint64_t seed, float mean, float std, void* stream);
+
+/* max over i of |got - ref| / (|ref| + 1) with ref fp32; result[0] gets the
+ * maximum.  `scratch` holds 1024 floats. */
+int tcl_max_rel_err(const void* got_bf16, const float* ref, int64_t n, float* scratch,
+                    float* result, void* stream);
+
+const char* tcl_status_string(int code);
+
+#ifdef __cplusplus
+}
+#endif

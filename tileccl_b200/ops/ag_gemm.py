@@ -1,0 +1,79 @@
+"""Fused all-gather -> GEMM (tensor-parallel column-parallel linear).
+
+Every rank holds a row shard ``A_r`` [M/world, K] and a local ``Bt`` [N_local,
+K]; the result on every rank is ``concat_r(A_r) @ Bt.T`` = [M, N_local].  The
+shard lives inside the rank's gathered buffer (symmetric heap), so the local
+part needs no copy; gather warps of the GEMM kernel pull the peers' shards with
+P2P loads and the TMA producer starts on a row block as soon as its counter
+says it has landed.  ``gather_rows`` is the granularity of those counters.
+
+Reference parity: comm_comp/exp2_ag_gemm_granularity.cu:168-300 (the
+segmented-launch + copy-engine pipeline; its chunk count S is this op's
+``gather_rows``), and :15-20 of that file for the in-kernel form built here.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _native
+from ..parallel.heap import SymmetricHeap
+from ._plan import Plan, require_bf16_rowmajor
+
+
+class AgGemm:
+    def __init__(self, heap: SymmetricHeap, M: int, K: int, Bt: torch.Tensor, cta_group: int = 2,
+                 gather_rows: int = 512, out: torch.Tensor | None = None, group_m: int = 0,
+                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0):
+        require_bf16_rowmajor(Bt, "Bt")
+        self.heap = heap
+        world, rank = heap.world, heap.rank
+        N = Bt.shape[0]
+        if Bt.shape[1] != K:
+            raise ValueError("Bt must be [N, K]")
+        seg = M // world
+        if M % world or seg % (128 * cta_group):
+            raise ValueError("M / world must be a multiple of 128 * cta_group")
+        gather_rows = min(gather_rows, seg)
+        self.a_full = heap.empty((M, K), torch.bfloat16)
+        self.flags = heap.zeros((M // 128 + 32,), torch.int32)
+        self.done = heap.zeros((32,), torch.int32)       # [0] gather warps done, [16] peers done reading
+        self.barrier = heap.zeros((32,), torch.int32)
+        self.a_shard = self.a_full[rank * seg:(rank + 1) * seg]
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=Bt.device)
+        self.out = out
+        d = _native.GemmDesc()
+        d.mode, d.cta_group = _native.MODE_AG_GEMM, cta_group
+        d.M, d.N, d.K = M, N, K
+        d.lda, d.ldb, d.ldc = K, Bt.stride(0), out.stride(0)
+        d.A, d.B = self.a_full.data_ptr(), Bt.data_ptr()
+        d.world, d.rank = world, rank
+        d.seg_rows = M            # the output is one local segment
+        d.comm_enabled = 1 if comm_enabled else 0
+        d.dst_base[0] = out.data_ptr()
+        d.dst_row_off[0] = 0
+        d.seg_rows = seg
+        for s in range(world):
+            d.dst_base[s] = out.data_ptr()
+            d.dst_row_off[s] = s * seg
+            d.ag_src[s] = heap.peer_ptr(self.a_full, s) + s * seg * K * 2
+            d.ag_read_done[s] = heap.peer_ptr(self.done, s) + 16 * 4
+            d.barrier[s] = heap.peer_ptr(self.barrier, s)
+        d.ag_flags = self.flags.data_ptr()
+        d.gather_rows = gather_rows
+        d.ag_done = self.done.data_ptr()
+        d.timeout_ns = int(timeout_ms * 1e6)
+        d.group_m, d.num_ctas = group_m, num_ctas
+        self.plan = Plan(d, keep_alive=(Bt, out, self.a_full, self.flags, self.done, self.barrier))
+        self.gather_rows = gather_rows
+
+    def __call__(self, stream=None) -> torch.Tensor:
+        self.plan.run(stream)
+        return self.out
+
+    def check(self) -> None:
+        self.plan.check()
+
+    @property
+    def launches(self) -> int:
+        return self.plan.launches

@@ -1,0 +1,57 @@
+"""Plain bf16 GEMM on the tcgen05 kernel: ``D = A @ Bt.T``.
+
+``A`` is [M, K], ``Bt`` is [N, K] (the K-major "column-major B[K, N]" that the
+reference's GEMM takes, comm_comp/gemm_sm90.cuh:40-46), ``D`` is [M, N].  This
+is the in-repo control GEMM; the baseline GEMM is cuBLAS (``torch.matmul``).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _native
+from ._plan import Plan, require_bf16_rowmajor
+
+
+class GemmPlan(Plan):
+    def __init__(self, A: torch.Tensor, Bt: torch.Tensor, out: torch.Tensor | None = None,
+                 cta_group: int = 2, group_m: int = 0, num_ctas: int = 0, timeout_ms: float = 4000.0,
+                 dst_ptrs: list[int] | None = None, seg_rows: int | None = None):
+        """``dst_ptrs``/``seg_rows`` route row segments of D to other addresses
+        (a peer's buffer): the epilogue-remote experiment."""
+        require_bf16_rowmajor(A, "A")
+        require_bf16_rowmajor(Bt, "Bt")
+        M, K = A.shape
+        N, K2 = Bt.shape
+        if K2 != K:
+            raise ValueError("A is [M, K] and Bt is [N, K]: K differs")
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=A.device)
+        require_bf16_rowmajor(out, "out")
+        d = _native.GemmDesc()
+        d.mode, d.cta_group = _native.MODE_PLAIN, cta_group
+        d.M, d.N, d.K = M, N, K
+        d.lda, d.ldb, d.ldc = A.stride(0), Bt.stride(0), out.stride(0)
+        d.A, d.B = A.data_ptr(), Bt.data_ptr()
+        d.world, d.rank = 1, 0
+        d.seg_rows = seg_rows or M
+        nseg = M // d.seg_rows
+        for s in range(nseg):
+            d.dst_base[s] = dst_ptrs[s] if dst_ptrs else out.data_ptr()
+            # With an explicit pointer per segment the segment starts at row 0 of it.
+            d.dst_row_off[s] = 0 if dst_ptrs else s * d.seg_rows
+        d.timeout_ns = int(timeout_ms * 1e6)
+        d.group_m, d.num_ctas = group_m, num_ctas
+        super().__init__(d, keep_alive=(A, Bt, out))
+        self.out = out
+
+    def __call__(self, stream=None) -> torch.Tensor:
+        self.run(stream)
+        return self.out
+
+
+def gemm(A: torch.Tensor, Bt: torch.Tensor, cta_group: int = 2) -> torch.Tensor:
+    """One-shot convenience wrapper (builds a plan per call)."""
+    plan = GemmPlan(A, Bt, cta_group=cta_group)
+    out = plan()
+    plan.check()
+    return out
