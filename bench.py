@@ -1,0 +1,255 @@
+#!/usr/bin/env python
+"""Headline benchmark: fused GEMM->reduce-scatter and all-gather->GEMM against
+NCCL + cuBLAS on the same GPUs.
+
+One step = one fused GEMM+RS (global M=32768, N=8192, K=8192 sharded over the
+N GPUs) followed by one fused AG+GEMM (A shard [32768/N, 8192], local B
+[8192, 28672/N]); bf16 N(0,1) activations, N(0,0.02) AG weights, synthetic.
+The same step is also timed on the baseline path (torch.matmul = cuBLAS, then /
+preceded by the NCCL collective).  Every time is device-timed with CUDA events
+and reported as the max over ranks; the L2 is flushed between timed steps.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \\
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+Prints one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+REF_UNAVAILABLE = ("reference is 13 stand-alone CUDA programs, not an installable package (pip: neither setup.py "
+                   "nor pyproject.toml); its GEMM+RS / AG+GEMM programs need the empty CUTLASS submodule and are "
+                   "sm_90a wgmma kernels that cannot run on sm_100")
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="tileccl", choices=["tileccl", "reference"])
+    ap.add_argument("--m", type=int, default=32768)
+    ap.add_argument("--n-rs", type=int, default=8192)
+    ap.add_argument("--k-rs", type=int, default=8192, help="global K of the GEMM+RS, sharded over the GPUs")
+    ap.add_argument("--k-ag", type=int, default=8192)
+    ap.add_argument("--n-ag", type=int, default=28672, help="global N of the AG+GEMM, sharded over the GPUs")
+    ap.add_argument("--gather-rows", type=int, default=512)
+    ap.add_argument("--cta-group", type=int, default=2)
+    ap.add_argument("--no-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from tileccl_b200 import _native
+    from tileccl_b200.ops import baseline as base
+    from tileccl_b200.ops import elementwise as ew
+    from tileccl_b200.ops.ag_gemm import AgGemm
+    from tileccl_b200.ops.gemm_rs import GemmRs
+    from tileccl_b200.parallel import group as G
+    from tileccl_b200.parallel.heap import SymmetricHeap
+    from tileccl_b200.utils import roofline
+    from tileccl_b200.utils.clocks import ClockSampler
+    from tileccl_b200.utils.timing import L2Flusher
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    _native.lib()  # fail loudly if the native library is missing
+
+    rank, world, local = G.init()
+    # Clock / throttle sampling runs from here to the end of the fused timing;
+    # the summary keeps the samples taken under load.
+    sampler = ClockSampler(gpu_index=local).start() if rank == 0 else None
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE is {world}", file=sys.stderr)
+    tp = world
+    M = args.m
+    N_rs, K_rs = args.n_rs, args.k_rs // tp
+    K_ag, N_ag = args.k_ag, args.n_ag // tp
+    steps, warmup = args.steps, max(3, args.warmup)
+    dev = torch.device("cuda", torch.cuda.current_device())
+
+    heap_bytes = 2 * (M * N_rs * 2 + (M // tp) * N_rs * 2 + M * K_ag * 2) + (64 << 20)
+    heap = SymmetricHeap(heap_bytes)
+
+    # Inputs: synthetic, seeded per rank.
+    A_rs = torch.empty(M, K_rs, dtype=torch.bfloat16, device=dev)
+    Bt_rs = torch.empty(N_rs, K_rs, dtype=torch.bfloat16, device=dev)
+    Bt_ag = torch.empty(N_ag, K_ag, dtype=torch.bfloat16, device=dev)
+    ew.fill_normal_(A_rs, seed=10 + rank)
+    ew.fill_normal_(Bt_rs, seed=110 + rank)
+    ew.fill_normal_(Bt_ag, seed=210 + rank, std=0.02)
+    rs = GemmRs(heap, A_rs, Bt_rs, cta_group=args.cta_group)
+    ag = AgGemm(heap, M, K_ag, Bt_ag, cta_group=args.cta_group, gather_rows=args.gather_rows)
+    ew.fill_normal_(ag.a_shard, seed=310 + rank)
+    torch.cuda.synchronize()
+    G.host_barrier()
+
+    def fused_step():
+        rs()
+        ag()
+
+    # Baseline path (cuBLAS + NCCL), same inputs.
+    run_base = not args.no_baseline
+    if run_base:
+        full = torch.empty(M, N_rs, dtype=torch.bfloat16, device=dev)
+        out_b = torch.empty(M // tp, N_rs, dtype=torch.bfloat16, device=dev) if tp > 1 else full
+        gathered = torch.empty(M, K_ag, dtype=torch.bfloat16, device=dev) if tp > 1 else None
+        out_ag_b = torch.empty(M, N_ag, dtype=torch.bfloat16, device=dev)
+        shard_b = ag.a_shard.clone()
+
+        def base_rs():
+            return base.gemm_rs_baseline(A_rs, Bt_rs, out=out_b if tp > 1 else None, full=full)
+
+        def base_ag():
+            return base.ag_gemm_baseline(shard_b, Bt_ag, gathered=gathered, out=out_ag_b)
+
+    # ---- verification (untimed): fused vs baseline on the full outputs ----
+    verified = None
+    fused_step()
+    rs.check()
+    ag.check()
+    if run_base:
+        ob = base_rs()
+        oa = base_ag()
+        torch.cuda.synchronize()
+        # bf16 partials/NCCL both round at the partials' magnitude: compare on that scale.
+        scale = float(K_rs * tp) ** 0.5
+        e_rs = ((rs.out.float() - ob.float()).abs().max() / scale).item()
+        e_ag = ((ag.out.float() - oa.float()).abs() / (oa.float().abs() + 1)).max().item()
+        verified = bool(e_rs < 0.05 and e_ag < 0.02)
+        errs = {"gemm_rs_max_abs_over_sqrtK": e_rs, "ag_gemm_max_rel": e_ag}
+    else:
+        errs = {}
+
+    flush = L2Flusher()
+
+    def timed(fn_list, n_steps, n_warm):
+        """Per-step device times (us) of each function in fn_list, run back to back."""
+        for _ in range(n_warm):
+            for f in fn_list:
+                f()
+        torch.cuda.synchronize()
+        G.host_barrier()
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(fn_list) + 1)] for _ in range(n_steps)]
+        for i in range(n_steps):
+            flush()
+            ev[i][0].record()
+            for j, f in enumerate(fn_list):
+                f()
+                ev[i][j + 1].record()
+        torch.cuda.synchronize()
+        G.host_barrier()
+        per = [[ev[i][j].elapsed_time(ev[i][j + 1]) * 1e3 for i in range(n_steps)] for j in range(len(fn_list))]
+        return per
+
+    launches0 = rs.launches + ag.launches
+    per = timed([rs, ag], steps, warmup)
+    gpu_launches = rs.launches + ag.launches - launches0 - 2 * warmup
+    clocks = sampler.summary() if sampler else None
+    rs.check()
+    ag.check()
+    rs_us = G.max_over_ranks(sum(per[0]) / steps)
+    ag_us = G.max_over_ranks(sum(per[1]) / steps)
+    step_us = G.max_over_ranks(sum(a + b for a, b in zip(per[0], per[1])) / steps)
+
+    b_rs_us = b_ag_us = b_step_us = None
+    if run_base:
+        perb = timed([base_rs, base_ag], steps, warmup)
+        b_rs_us = G.max_over_ranks(sum(perb[0]) / steps)
+        b_ag_us = G.max_over_ranks(sum(perb[1]) / steps)
+        b_step_us = G.max_over_ranks(sum(a + b for a, b in zip(perb[0], perb[1])) / steps)
+
+    # ---- end to end through the public API: H2D of the step's inputs from pinned
+    # memory, the two fused ops, D2H of a result metric, every step ----
+    e2e = None
+    if not args.no_e2e:
+        a_host = torch.empty(M, K_rs, dtype=torch.bfloat16).pin_memory()
+        x_host = torch.empty(M // tp, K_ag, dtype=torch.bfloat16).pin_memory()
+        a_host.copy_(A_rs)
+        x_host.copy_(ag.a_shard)
+        metric_host = torch.empty(2, dtype=torch.float32).pin_memory()
+
+        def e2e_step():
+            A_rs.copy_(a_host, non_blocking=True)
+            ag.a_shard.copy_(x_host, non_blocking=True)
+            rs()
+            ag()
+            m = torch.stack([rs.out[0].float().sum(), ag.out[0].float().sum()])
+            metric_host.copy_(m, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return float(metric_host[0]) + float(metric_host[1])
+
+        for _ in range(3):
+            e2e_step()
+        torch.cuda.synchronize()
+        G.host_barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / steps * 1e6
+        G.host_barrier()
+        e2e = {"value": G.max_over_ranks(dt), "unit": "us_per_step",
+               "h2d_bytes_per_step": a_host.numel() * 2 + x_host.numel() * 2,
+               "d2h_bytes_per_step": metric_host.numel() * 4}
+        rs.check()
+        ag.check()
+
+    roof_rs = roofline.gemm_rs_roofline_us(M, N_rs, K_rs, tp)
+    roof_ag = roofline.ag_gemm_roofline_us(M, N_ag, K_ag, tp)
+    roof_us = roof_rs["roofline_us"] + roof_ag["roofline_us"]
+    flops = 2.0 * M * N_rs * K_rs * tp + 2.0 * M * N_ag * K_ag * tp
+
+    if rank == 0:
+        out = {
+            "metric": "fused GEMM+RS + AG+GEMM step time (device-timed, max over ranks)",
+            "value": round(step_us, 2), "unit": "us_per_step", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": round(step_us / 1e3, 4), "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1) bf16 activations, N(0,0.02) AG weights, random init",
+            "config": {"model": "flux-style TP GEMM pair (Llama-3-70B MLP shapes)",
+                       "gemm_rs": {"M": M, "N": N_rs, "K_global": args.k_rs, "K_per_rank": K_rs},
+                       "ag_gemm": {"M": M, "K": K_ag, "N_global": args.n_ag, "N_per_rank": N_ag, "gather_rows": args.gather_rows},
+                       "global_batch": M, "seq_len": None, "parallelism": f"tp{tp}", "cta_group": args.cta_group,
+                       "l2": "flushed between timed steps (256 MiB write); inputs also exceed L2"},
+            "gemm_rs_us": round(rs_us, 2), "ag_gemm_us": round(ag_us, 2),
+            "nccl_cublas_us": None if b_step_us is None else round(b_step_us, 2),
+            "nccl_cublas_gemm_rs_us": None if b_rs_us is None else round(b_rs_us, 2),
+            "nccl_cublas_ag_gemm_us": None if b_ag_us is None else round(b_ag_us, 2),
+            "speedup_vs_nccl_cublas": None if b_step_us is None else round(b_step_us / step_us, 4),
+            "speedup_gemm_rs": None if b_rs_us is None else round(b_rs_us / rs_us, 4),
+            "speedup_ag_gemm": None if b_ag_us is None else round(b_ag_us / ag_us, 4),
+            "tflops_aggregate": round(flops / (step_us * 1e-6) / 1e12, 1),
+            "roofline_us": round(roof_us, 2),
+            "roofline": {"gemm_rs": roof_rs, "ag_gemm": roof_ag, "of": roof_rs["peaks"] + " (sustained cuBLAS bf16, 770 GB/s NVLink per direction)"},
+            "pct_roofline": round(100.0 * roof_us / step_us, 1),
+            "pct_roofline_gemm_rs": round(100.0 * roof_rs["roofline_us"] / rs_us, 1),
+            "pct_roofline_ag_gemm": round(100.0 * roof_ag["roofline_us"] / ag_us, 1),
+            "verified": verified, "verify_errors": errs,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": gpu_launches, "impl": "tileccl_b200",
+        }
+        print(json.dumps(out), flush=True)
+    torch.cuda.synchronize()
+    G.host_barrier()
+    heap.close()
+    G.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,135 @@
+"""Worker of the multi-GPU tests: run as one process per GPU by torchrun.
+
+Each check compares a fused op against a plain PyTorch fp32 computation on the
+all-gathered inputs.  Prints ``WORKER_OK`` on rank 0 when every check passed.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from tileccl_b200.models.tp_mlp import TpMlp  # noqa: E402
+from tileccl_b200.ops import elementwise as ew  # noqa: E402
+from tileccl_b200.ops.ag_gemm import AgGemm  # noqa: E402
+from tileccl_b200.ops.gemm_rs import GemmRs  # noqa: E402
+from tileccl_b200.parallel import group as G  # noqa: E402
+from tileccl_b200.parallel.heap import SymmetricHeap  # noqa: E402
+
+
+def rel(out, ref):
+    return ((out.float() - ref).abs() / (ref.abs() + 1)).max().item()
+
+
+def gather(t):
+    out = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, t.contiguous())
+    return out
+
+
+def main():
+    rank, world, _ = G.init()
+    torch.manual_seed(100 + rank)
+    heap = SymmetricHeap(512 << 20)
+    fails = []
+
+    # heap symmetry: a peer's view of a tensor shows what that peer wrote
+    t = heap.empty((1024,), torch.int32)
+    t.fill_(rank + 1)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for r in range(world):
+        v = heap.peer_tensor(t, r)
+        if int(v[0]) != r + 1 or int(v[-1]) != r + 1:
+            fails.append(f"heap view of rank {r} wrong")
+    dist.barrier()
+
+    # device barrier epochs
+    bar = ew.DeviceBarrier(heap, timeout_ms=2000)
+    for _ in range(5):
+        bar()
+    torch.cuda.synchronize()
+    bar.check()
+
+    for cta_group in (1, 2):
+        # ---- fused GEMM + reduce-scatter ----
+        M, N, K = 256 * cta_group * world * 2, 512, 320
+        A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        op = GemmRs(heap, A, Bt, cta_group=cta_group, timeout_ms=2000)
+        As, Bs = gather(A), gather(Bt)
+        parts = [a.float() @ b.float().t() for a, b in zip(As, Bs)]
+        ref = sum(parts)
+        seg = M // world
+        sl = slice(rank * seg, (rank + 1) * seg)
+        # The partials cross NVLink as bf16 and are summed in fp32: every
+        # partial and the result are rounded once (bf16 unit round-off = 2^-8 relative).
+        bound = 2.0 ** -8 * 1.05 * (sum(p.abs() for p in parts) + ref.abs())[sl] + 1e-2
+        for it in range(3):
+            out = op()
+            op.check()
+            excess = ((out.float() - ref[sl]).abs() - bound).max().item()
+            if excess > 0:
+                fails.append(f"gemm_rs g{cta_group} iter {it}: error exceeds the bf16 rounding bound by {excess}")
+            op.stage.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+
+        # ---- fused all-gather + GEMM ----
+        M, N, K = 256 * cta_group * world, 768, 512
+        Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        for gather_rows in (128, 256 * cta_group):
+            op = AgGemm(heap, M, K, Bt, cta_group=cta_group, gather_rows=gather_rows, timeout_ms=2000)
+            for it in range(3):
+                shard = torch.randn(M // world, K, device="cuda", dtype=torch.bfloat16)
+                # poison the peers' part of the gathered buffer: stale rows must not be used
+                op.a_full.fill_(float("nan"))
+                op.a_shard.copy_(shard)
+                torch.cuda.synchronize()
+                dist.barrier()
+                out = op()
+                op.check()
+                full = torch.cat(gather(shard), 0)
+                e = rel(out, full.float() @ Bt.float().t())
+                if e > 2e-2 or not torch.equal(op.a_full, full):
+                    fails.append(f"ag_gemm g{cta_group} rows {gather_rows} iter {it}: rel err {e}")
+                dist.barrier()
+
+    # ---- MLP block ----
+    tokens, hidden, ffn = 512 * world, 512, 1024 * world
+    mlp = TpMlp(heap, tokens, hidden, ffn, cta_group=2, gather_rows=256)
+    x = torch.randn(tokens // world, hidden, device="cuda", dtype=torch.bfloat16)
+    mlp.x_shard.copy_(x)
+    torch.cuda.synchronize()
+    dist.barrier()
+    y = mlp()
+    mlp.check()
+    xf = torch.cat(gather(x), 0).float()
+    f = ffn // world
+    parts = []
+    for wgu, wd in zip(gather(mlp.w_gate_up), gather(mlp.w_down)):
+        h = (xf @ wgu.float().t()).bfloat16().float()
+        a = (torch.nn.functional.silu(h[:, :f]) * h[:, f:]).bfloat16().float()
+        parts.append(a @ wd.float().t())
+    ref = sum(parts)[rank * (tokens // world):(rank + 1) * (tokens // world)]
+    e = rel(y, ref)
+    if e > 2e-2:
+        fails.append(f"tp_mlp rel err {e}")
+
+    flag = torch.tensor([len(fails)], device="cuda")
+    dist.all_reduce(flag)
+    if fails:
+        print(f"[rank {rank}] FAILURES: {fails}", flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    heap.close()
+    if rank == 0 and int(flag) == 0:
+        print("WORKER_OK", flush=True)
+    G.shutdown()
+    sys.exit(1 if int(flag) else 0)
+
+
+if __name__ == "__main__":
+    main()

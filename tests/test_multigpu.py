@@ -1,0 +1,26 @@
+"""Fused ops across real GPUs (2, 4, 8 where present): one process per GPU."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(world: int, port: int):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "_mp_worker.py")]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_ops_multi_gpu(native_lib, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    r = _run(world, 29600 + world)
+    assert r.returncode == 0 and "WORKER_OK" in r.stdout, r.stdout[-4000:] + r.stderr[-4000:]

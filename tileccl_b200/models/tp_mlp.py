@@ -1,0 +1,69 @@
+"""Tensor-parallel gated-SiLU MLP block (Llama-3-70B shaped by default),
+sequence-sharded activations in and out:
+
+    x_shard [T/tp, H] --AG+GEMM(gate|up)--> [T, 2F/tp] --SiLU*mul--> [T, F/tp]
+                      --GEMM+RS(down)----> y_shard [T/tp, H]
+
+Three kernel launches per forward: the fused all-gather GEMM, the fused
+SiLU*mul, the fused GEMM reduce-scatter.  The reference has no model; this is
+the end-to-end pipeline named by the benchmark configuration (hidden 8192, ffn
+28672, 16384 tokens, tp = 8).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import elementwise as ew
+from ..ops.ag_gemm import AgGemm
+from ..ops.gemm_rs import GemmRs
+from ..parallel.heap import SymmetricHeap
+
+
+def heap_bytes(tokens: int, hidden: int, ffn: int, world: int) -> int:
+    """Symmetric-heap bytes one :class:`TpMlp` takes per rank."""
+    f = ffn // world
+    return (tokens * hidden * 2            # gathered x
+            + tokens * hidden * 2          # RS staging
+            + tokens // world * hidden * 2 # RS output
+            + (4 << 20))
+
+
+class TpMlp:
+    def __init__(self, heap: SymmetricHeap, tokens: int, hidden: int = 8192, ffn: int = 28672,
+                 cta_group: int = 2, gather_rows: int = 512, seed: int = 0, init_std: float = 0.02):
+        world, rank = heap.world, heap.rank
+        if ffn % world or tokens % world:
+            raise ValueError("ffn and tokens must be divisible by the world size")
+        f = ffn // world
+        self.tokens, self.hidden, self.ffn_local = tokens, hidden, f
+        dev = torch.device("cuda", torch.cuda.current_device())
+        # Weights in the K-major layout the kernels take: [out_features, in_features].
+        self.w_gate_up = torch.empty(2 * f, hidden, dtype=torch.bfloat16, device=dev)   # rows: gate | up
+        self.w_down = torch.empty(hidden, f, dtype=torch.bfloat16, device=dev)
+        ew.fill_normal_(self.w_gate_up, seed=seed * 1000 + 2 * rank, std=init_std)
+        ew.fill_normal_(self.w_down, seed=seed * 1000 + 2 * rank + 1, std=init_std)
+        self.h = torch.empty(tokens, 2 * f, dtype=torch.bfloat16, device=dev)
+        self.act = torch.empty(tokens, f, dtype=torch.bfloat16, device=dev)
+        self.ag = AgGemm(heap, tokens, hidden, self.w_gate_up, cta_group=cta_group,
+                         gather_rows=gather_rows, out=self.h)
+        self.rs = GemmRs(heap, self.act, self.w_down, cta_group=cta_group)
+
+    @property
+    def x_shard(self) -> torch.Tensor:
+        """This rank's [T/tp, H] input slot inside the gathered buffer; write the input here."""
+        return self.ag.a_shard
+
+    def forward(self, stream=None) -> torch.Tensor:
+        self.ag(stream)
+        ew.silu_mul(self.h, self.act, stream)
+        return self.rs(stream)
+
+    __call__ = forward
+
+    def check(self) -> None:
+        self.ag.check()
+        self.rs.check()
+
+    @property
+    def launches(self) -> int:
+        return self.ag.launches + self.rs.launches + self.ag.launches  # ag, silu_mul (one per forward), rs

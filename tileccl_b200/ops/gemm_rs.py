@@ -59,9 +59,18 @@ class GemmRs:
         d.A, d.B = A.data_ptr(), Bt.data_ptr()
         d.world, d.rank = world, rank
         d.seg_rows = seg
+        if world == 1 and comm_enabled:
+            # One rank: nothing to reduce, the epilogue writes the result itself.
+            comm_enabled = False
+            self._direct = True
+        else:
+            self._direct = False
         d.comm_enabled = 1 if comm_enabled else 0
         for s in range(world):
-            if comm_enabled:
+            if self._direct:
+                d.dst_base[s] = self.out.data_ptr()
+                d.dst_row_off[s] = 0
+            elif comm_enabled:
                 # Segment s goes to rank s's staging, slot `rank`.
                 d.dst_base[s] = heap.peer_ptr(self.stage, s)
                 d.dst_row_off[s] = rank * seg
