@@ -121,7 +121,7 @@ def test_wait_runs_out_and_reports_status(native_lib):
     plan.run()
     with pytest.raises(KernelTimeout) as ei:
         plan.check()
-    assert ei.value.code == 5               # nobody else ever arrives at the start barrier
+    assert ei.value.code in (5, 6)          # the start barrier or a tile counter, whichever gave up first
     # the device still works
     x = torch.ones(8, device="cuda")
     assert float((x * 2).sum()) == 16.0

@@ -1,0 +1,77 @@
+"""Shared plumbing of the Python experiment drivers (one process per GPU)."""
+from __future__ import annotations
+
+import argparse
+import os
+
+import torch
+
+from ..ops import elementwise as ew
+from ..parallel import group as G
+from ..utils.stats import make_stats
+
+
+def parse_shape(text: str) -> tuple[int, int, int]:
+    """``N`` -> (N, N, N); ``MxNxK`` -> (M, N, K)  (comm_comp/common.cuh:80-105)."""
+    parts = text.lower().split("x")
+    if len(parts) == 1:
+        v = parse_size(parts[0])
+        return v, v, v
+    if len(parts) != 3:
+        raise argparse.ArgumentTypeError(f"bad shape {text!r}: want N or MxNxK")
+    return tuple(parse_size(p) for p in parts)  # type: ignore[return-value]
+
+
+def parse_size(text: str) -> int:
+    """Integer with an optional K/M/G suffix, powers of 1024 (comm_comp/common.cuh:52-66)."""
+    t = text.strip()
+    mult = 1
+    if t and t[-1].upper() in "KMG":
+        mult = 1024 ** ("KMG".index(t[-1].upper()) + 1)
+        t = t[:-1]
+    try:
+        return int(float(t) * mult)
+    except ValueError as e:
+        raise argparse.ArgumentTypeError(f"bad size {text!r}") from e
+
+
+def split_csv(text: str) -> list[str]:
+    return [p for p in (x.strip() for x in text.split(",")) if p]
+
+
+def timed_series(fn, iters: int, warmup: int, before=None, flush=None) -> list[float]:
+    """Device time of each of ``iters`` calls in microseconds; ``before`` (e.g. a
+    device barrier) and ``flush`` run untimed ahead of every call."""
+    for _ in range(warmup):
+        if before:
+            before()
+        fn()
+    torch.cuda.synchronize()
+    G.host_barrier()
+    s = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    for i in range(iters):
+        if flush:
+            flush()
+        if before:
+            before()
+        s[i].record()
+        fn()
+        e[i].record()
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) * 1e3 for a, b in zip(s, e)]
+
+
+def stats_of(series):
+    return make_stats(series)
+
+
+def device_line() -> str:
+    p = torch.cuda.get_device_properties(torch.cuda.current_device())
+    return f"{p.name}, {p.multi_processor_count} SMs, {p.total_memory / 2**30:.0f} GiB, cc {p.major}.{p.minor}"
+
+
+def out_path(path: str | None) -> str | None:
+    if path:
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    return path

@@ -17,12 +17,13 @@
 // A is [M, K] row-major, B is [N, K] row-major (the "column-major B[K, N]" of
 // the reference), D is row-major.  fp32 accumulation, bf16 output.
 //
-// Warp roles (320 threads, one CTA per SM):
+// Warp roles (352 threads, one CTA per SM):
 //   warp 0      TMA producer (one lane)
 //   warp 1      TMEM allocation + tcgen05.mma issue (one lane, leader CTA only)
 //   warps 2-5   epilogue: tcgen05.ld -> bf16 -> swizzled smem transpose ->
 //               coalesced 16-byte global stores (local or peer)
 //   warps 6-9   communication: reduce warps (GEMM+RS) or gather warps (AG+GEMM)
+//   warp 10     GEMM+RS signalling: publishes finished tiles to their owners
 //
 // kCtaGroup = 2 pairs two CTAs (a 2x1 cluster) on one 256x256 tile: each CTA
 // loads its own 128 rows of A and its own 128 rows of B (no multicast), the
@@ -80,6 +81,7 @@ struct GemmParams {
   int world, rank;
   int epoch;      // 1-based call number of the plan that owns the flag buffers
   int comm_enabled;
+  int ablate;     // experiment knobs: bit 0 = no reduce warps, bit 1 = no tile signals (timing only)
 
   // Output routing.  Rows are split in segments of seg_rows; row r of segment
   // s goes to dst_base[s] + (dst_row_off[s] + r - s * seg_rows) * ldc.
@@ -125,7 +127,8 @@ struct GemmCfg {
   static constexpr int EPI_BUF_BYTES = 32 * EPI_CHUNK_COLS * 2;   // 4 KiB
   static constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES; // double buffered
   static constexpr int COMM_WARPS = 4;
-  static constexpr int THREADS = (2 + EPI_WARPS + COMM_WARPS) * 32;
+  static constexpr int SIGNAL_WARP = 2 + EPI_WARPS + COMM_WARPS;  // index of the signalling warp
+  static constexpr int THREADS = (3 + EPI_WARPS + COMM_WARPS) * 32;
   static constexpr int TMEM_COLS = 512;             // two accumulator buffers of BN columns
   static constexpr int CTRL_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES + 1024;
@@ -142,6 +145,54 @@ __device__ __forceinline__ void report(const GemmParams& p, volatile int* s_abor
     p.status[3] = d1;
   }
   *s_abort = 1;
+}
+
+// Sums the `kWorld` staged bf16 partials of one 128x256 tile in fp32 and writes
+// the bf16 result.  128 threads; a thread owns one 16-byte column chunk and
+// walks rows 4 apart.  kRows rows are in flight per thread (kRows * kWorld
+// independent 16-byte loads) so that the loop is bandwidth- not latency-bound.
+template <int kWorld, int kRows>
+__device__ __forceinline__ void reduce_tile(const __nv_bfloat16* __restrict__ stage, size_t slot_elems,
+                                            size_t tile_off, int ldn, __nv_bfloat16* __restrict__ out,
+                                            size_t out_off, int ld_out, int ctid, int world_rt) {
+  const int world = kWorld > 0 ? kWorld : world_rt;
+  constexpr int kMaxW = kWorld > 0 ? kWorld : 8;
+  const int r_base = ctid >> 5;  // 0..3
+#pragma unroll 1
+  for (int pass = 0; pass < 32; pass += kRows) {
+    uint4 w[kRows][kMaxW];
+#pragma unroll
+    for (int j = 0; j < kRows; ++j) {
+      const size_t row_off = static_cast<size_t>((pass + j) * 4 + r_base) * ldn;
+#pragma unroll
+      for (int src = 0; src < kMaxW; ++src) {
+        if (src < world) w[j][src] = ptx::ld_v4_stream(stage + src * slot_elems + tile_off + row_off);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kRows; ++j) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+      for (int src = 0; src < kMaxW; ++src) {
+        if (src < world) {
+          const uint32_t u[4] = {w[j][src].x, w[j][src].y, w[j][src].z, w[j][src].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[2 * e] += __uint_as_float(u[e] << 16);
+            acc[2 * e + 1] += __uint_as_float(u[e] & 0xffff0000u);
+          }
+        }
+      }
+      uint4 o;
+      o.x = ptx::pack_bf16x2(__float_as_uint(acc[0]), __float_as_uint(acc[1]));
+      o.y = ptx::pack_bf16x2(__float_as_uint(acc[2]), __float_as_uint(acc[3]));
+      o.z = ptx::pack_bf16x2(__float_as_uint(acc[4]), __float_as_uint(acc[5]));
+      o.w = ptx::pack_bf16x2(__float_as_uint(acc[6]), __float_as_uint(acc[7]));
+      ptx::st_v4(out + out_off + static_cast<size_t>((pass + j) * 4 + r_base) * ld_out, o);
+    }
+  }
 }
 
 }  // namespace detail
@@ -172,6 +223,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
   volatile uint32_t* s_tmem_ptr = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * Cfg::STAGES + 40);
   volatile int* s_abort = reinterpret_cast<volatile int*>(ctrl + 16 * Cfg::STAGES + 44);
   volatile int* s_bcast = reinterpret_cast<volatile int*>(ctrl + 16 * Cfg::STAGES + 48);
+  int* s_warps_done = reinterpret_cast<int*>(ctrl + 16 * Cfg::STAGES + 52);  // epilogue warp-tiles stored
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -198,6 +250,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
     mbar_init(bar_drain, 1);
     *s_abort = 0;
     *s_bcast = 0;
+    *s_warps_done = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -424,26 +477,26 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
       if (p.mode == kModeGemmRs && p.comm_enabled) {
-        // This warp's 32 rows of the tile are stored: one release at system
-        // scope publishes them to the owner.  Each of the four epilogue warps
-        // signals on its own (a tile is complete at world * 4 arrivals), so no
-        // CTA-wide barrier sits on the store path.
+        // This warp's 32 rows of the tile are stored.  Publishing them needs a
+        // fence at system scope, which waits for the peer's acknowledgements;
+        // that wait is taken by the signalling warp, not here, so that the
+        // stores of the next tile keep streaming.
         __syncwarp();
         if (lane == 0) {
-          const int seg_row = (row0 - seg * p.seg_rows) / Cfg::BM;
-          red_release_sys_add(p.rs_tile_cnt[seg] + seg_row * sched.n_tiles + n_blk, 1);
+          __threadfence_block();
+          atomicAdd(s_warps_done, 1);
         }
       }
     }
-  } else {
+  } else if (warp < Cfg::SIGNAL_WARP) {
     // ===== communication warps =====
     const int cw = warp - (2 + Cfg::EPI_WARPS);
     const int ctid = threadIdx.x - (2 + Cfg::EPI_WARPS) * 32;  // 0..127
-    if (p.mode == kModeGemmRs && p.comm_enabled) {
+    if (p.mode == kModeGemmRs && p.comm_enabled && !(p.ablate & 1)) {
       // ---- reduce warps: sum the `world` staged partials of each tile of this
       // rank's segment, in the order in which the producers complete them ----
       const int items = (p.seg_rows / Cfg::BM) * sched.n_tiles;
-      const int target = p.epoch * p.world * Cfg::EPI_WARPS;
+      const int target = p.epoch * p.world;
       const size_t slot_elems = static_cast<size_t>(p.seg_rows) * p.N;
       for (int j = blockIdx.x; j < items; j += gridDim.x) {
         if (ctid == 0) {
@@ -459,27 +512,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int n_blk = j - seg_row * sched.n_tiles;
         const int colc = ctid & 31;  // 16-byte column chunk of the 256-column tile
         const size_t tile_off = static_cast<size_t>(seg_row) * Cfg::BM * p.N + n_blk * Cfg::BN + colc * 8;
-#pragma unroll 2
-        for (int pass = 0; pass < Cfg::BM / 4; ++pass) {
-          const int r = pass * 4 + (ctid >> 5);
-          float acc[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-          for (int src = 0; src < p.world; ++src) {
-            const uint4 w = ld_v4_stream(p.rs_stage + src * slot_elems + tile_off + static_cast<size_t>(r) * p.N);
-            const uint32_t u[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              acc[2 * e] += __uint_as_float(u[e] << 16);
-              acc[2 * e + 1] += __uint_as_float(u[e] & 0xffff0000u);
-            }
-          }
-          uint4 o;
-          o.x = pack_bf16x2(__float_as_uint(acc[0]), __float_as_uint(acc[1]));
-          o.y = pack_bf16x2(__float_as_uint(acc[2]), __float_as_uint(acc[3]));
-          o.z = pack_bf16x2(__float_as_uint(acc[4]), __float_as_uint(acc[5]));
-          o.w = pack_bf16x2(__float_as_uint(acc[6]), __float_as_uint(acc[7]));
-          st_v4(p.rs_out + (static_cast<size_t>(seg_row) * Cfg::BM + r) * p.ld_out + n_blk * Cfg::BN + colc * 8, o);
+        const size_t out_off = static_cast<size_t>(seg_row) * Cfg::BM * p.ld_out + n_blk * Cfg::BN + colc * 8;
+        switch (p.world) {
+          case 1: detail::reduce_tile<1, 8>(p.rs_stage, slot_elems, tile_off, p.N, p.rs_out, out_off, p.ld_out, ctid, 1); break;
+          case 2: detail::reduce_tile<2, 8>(p.rs_stage, slot_elems, tile_off, p.N, p.rs_out, out_off, p.ld_out, ctid, 2); break;
+          case 4: detail::reduce_tile<4, 4>(p.rs_stage, slot_elems, tile_off, p.N, p.rs_out, out_off, p.ld_out, ctid, 4); break;
+          case 8: detail::reduce_tile<8, 2>(p.rs_stage, slot_elems, tile_off, p.N, p.rs_out, out_off, p.ld_out, ctid, 8); break;
+          default: detail::reduce_tile<0, 2>(p.rs_stage, slot_elems, tile_off, p.N, p.rs_out, out_off, p.ld_out, ctid, p.world); break;
         }
       }
     } else if (p.mode == kModeAgGemm && fused_comm) {
@@ -538,6 +577,37 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!wait_ge<true>(p.ag_read_done[p.rank], p.epoch * (p.world - 1), s_abort, deadline, &seen, 512)) {
             detail::report(p, s_abort, kErrAgEndBarrier, p.epoch * (p.world - 1), seen);
           }
+        }
+      }
+    }
+  }
+
+  else {
+    // ===== signalling warp (GEMM+RS) =====
+    // Walks the same tile sequence as the epilogue.  Whenever more tiles have
+    // been stored by all four epilogue warps, one fence at system scope orders
+    // every store observed so far, then each finished tile's owner gets +1 on
+    // the tile's counter.  One fence may cover several tiles.
+    if (p.mode == kModeGemmRs && p.comm_enabled && !(p.ablate & 2) && lane == 0) {
+      int signalled = 0;
+      int t = group_id;
+      unsigned spins = 0;
+      while (t < num_tiles) {
+        const int done = *reinterpret_cast<volatile int*>(s_warps_done) / Cfg::EPI_WARPS;
+        if (done > signalled) {
+          fence_sys();
+          for (; signalled < done && t < num_tiles; ++signalled, t += num_groups) {
+            int m_blk, n_blk;
+            sched.tile(t, &m_blk, &n_blk);
+            const int row0 = m_blk * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BM;
+            const int seg = row0 / p.seg_rows;
+            const int seg_row = (row0 - seg * p.seg_rows) / Cfg::BM;
+            red_relaxed_sys_add(p.rs_tile_cnt[seg] + seg_row * sched.n_tiles + n_blk, 1);
+          }
+          spins = 0;
+        } else {
+          __nanosleep(100);
+          if ((++spins & 63u) == 0u && (*s_abort != 0 || globaltimer_ns() > deadline)) break;
         }
       }
     }

@@ -228,6 +228,7 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
   p.M = d->M; p.N = d->N; p.K = d->K; p.ldc = d->ldc;
   p.world = d->world; p.rank = d->rank;
   p.comm_enabled = d->comm_enabled;
+  p.ablate = d->ablate;
   p.seg_rows = d->seg_rows;
   for (int s = 0; s < TCL_MAX_WORLD; ++s) {
     p.dst_base[s] = static_cast<__nv_bfloat16*>(d->dst_base[s]);
@@ -253,12 +254,15 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
     if (d->ldc != d->N) return fail("GEMM+RS: staging pitch (ldc) must equal N");
     sc.order = kOrderRsPush; sc.world = d->world; sc.rank = d->rank;
     const int st = sc.m_tiles / d->world;
-    int g = d->rs_chunks > 0 ? d->rs_chunks : 1;
+    // Default: one tile row per step (rs_chunks = tile rows of a segment) and a
+    // raster group that spans every segment, so that the tiles in flight at any
+    // instant target all owners evenly whatever the drift between ranks.
+    int g = d->rs_chunks > 0 ? d->rs_chunks : st;
     if (st % g != 0) return fail("GEMM+RS: rs_chunks must divide the tile rows of a segment");
     sc.rs_chunks = g;
     if (d->group_m <= 0) {
-      const int cpr = st / g;
-      sc.group_m = cpr < sc.group_m ? cpr : sc.group_m;
+      const int per = 8 / d->world > 0 ? 8 / d->world : 1;
+      sc.group_m = d->world * per;
     }
     if (d->comm_enabled) {
       if (!d->rs_stage || !d->rs_out || d->ld_out % 8 != 0 || d->ld_out < d->N)

@@ -27,7 +27,7 @@ def staging_bytes(M: int, N: int, world: int) -> int:
 class GemmRs:
     def __init__(self, heap: SymmetricHeap, A: torch.Tensor, Bt: torch.Tensor, cta_group: int = 2,
                  rs_chunks: int = 0, comm_enabled: bool = True, group_m: int = 0, num_ctas: int = 0,
-                 timeout_ms: float = 4000.0):
+                 timeout_ms: float = 4000.0, ablate: int = 0):
         require_bf16_rowmajor(A, "A")
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
@@ -40,13 +40,6 @@ class GemmRs:
         tile_m = 128 * cta_group
         if seg % tile_m:
             raise ValueError(f"M / world must be a multiple of {tile_m}")
-        seg_tiles = seg // tile_m
-        if rs_chunks <= 0:
-            rs_chunks = 1
-            for g in (8, 4, 2):
-                if seg_tiles % g == 0 and seg_tiles // g >= 1:
-                    rs_chunks = g
-                    break
         # Symmetric objects: staging [world][seg][N], per-tile counters, barrier counter.
         self.stage = heap.empty((world, seg, N), torch.bfloat16)
         self.tile_cnt = heap.zeros(((seg // 128) * (N // 256),), torch.int32)
@@ -86,6 +79,7 @@ class GemmRs:
         d.rs_chunks = rs_chunks
         d.timeout_ns = int(timeout_ms * 1e6)
         d.group_m, d.num_ctas = group_m, num_ctas
+        d.ablate = ablate
         self.plan = Plan(d, keep_alive=(A, Bt, self.stage, self.tile_cnt, self.barrier, self.out))
         self.rs_chunks = rs_chunks
 
