@@ -139,38 +139,48 @@ def main():
 
     flush = L2Flusher()
 
-    def timed(fn_list, n_steps, n_warm):
-        """Per-step device times (us) of each function in fn_list, run back to back."""
+    def timed(variants, n_steps, n_warm):
+        """variants: {name: [fn, ...]}.  Per-step device times (us) of each
+        function, one step of every variant in turn so that the fused path and
+        the baseline see the same clocks and temperature."""
+        names = list(variants)
         for _ in range(n_warm):
-            for f in fn_list:
-                f()
+            for n in names:
+                for f in variants[n]:
+                    f()
         torch.cuda.synchronize()
         G.host_barrier()
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(fn_list) + 1)] for _ in range(n_steps)]
+        ev = {n: [[torch.cuda.Event(enable_timing=True) for _ in range(len(variants[n]) + 1)]
+                  for _ in range(n_steps)] for n in names}
         for i in range(n_steps):
-            flush()
-            ev[i][0].record()
-            for j, f in enumerate(fn_list):
-                f()
-                ev[i][j + 1].record()
+            for n in names:
+                flush()
+                ev[n][i][0].record()
+                for j, f in enumerate(variants[n]):
+                    f()
+                    ev[n][i][j + 1].record()
         torch.cuda.synchronize()
         G.host_barrier()
-        per = [[ev[i][j].elapsed_time(ev[i][j + 1]) * 1e3 for i in range(n_steps)] for j in range(len(fn_list))]
-        return per
+        return {n: [[ev[n][i][j].elapsed_time(ev[n][i][j + 1]) * 1e3 for i in range(n_steps)]
+                    for j in range(len(variants[n]))] for n in names}
 
+    variants = {"fused": [rs, ag]}
+    if run_base:
+        variants["base"] = [base_rs, base_ag]
     launches0 = rs.launches + ag.launches
-    per = timed([rs, ag], steps, warmup)
+    res = timed(variants, steps, warmup)
     gpu_launches = rs.launches + ag.launches - launches0 - 2 * warmup
     clocks = sampler.summary() if sampler else None
     rs.check()
     ag.check()
+    per = res["fused"]
     rs_us = G.max_over_ranks(sum(per[0]) / steps)
     ag_us = G.max_over_ranks(sum(per[1]) / steps)
     step_us = G.max_over_ranks(sum(a + b for a, b in zip(per[0], per[1])) / steps)
 
     b_rs_us = b_ag_us = b_step_us = None
     if run_base:
-        perb = timed([base_rs, base_ag], steps, warmup)
+        perb = res["base"]
         b_rs_us = G.max_over_ranks(sum(perb[0]) / steps)
         b_ag_us = G.max_over_ranks(sum(perb[1]) / steps)
         b_step_us = G.max_over_ranks(sum(a + b for a, b in zip(perb[0], perb[1])) / steps)
@@ -226,7 +236,8 @@ def main():
                        "gemm_rs": {"M": M, "N": N_rs, "K_global": args.k_rs, "K_per_rank": K_rs},
                        "ag_gemm": {"M": M, "K": K_ag, "N_global": args.n_ag, "N_per_rank": N_ag, "gather_rows": args.gather_rows},
                        "global_batch": M, "seq_len": None, "parallelism": f"tp{tp}", "cta_group": args.cta_group,
-                       "l2": "flushed between timed steps (256 MiB write); inputs also exceed L2"},
+                       "l2": "flushed between timed steps (256 MiB write); inputs also exceed L2",
+                       "timing": "fused and NCCL+cuBLAS steps alternate inside one timed loop"},
             "gemm_rs_us": round(rs_us, 2), "ag_gemm_us": round(ag_us, 2),
             "nccl_cublas_us": None if b_step_us is None else round(b_step_us, 2),
             "nccl_cublas_gemm_rs_us": None if b_rs_us is None else round(b_rs_us, 2),

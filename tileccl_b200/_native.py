@@ -101,6 +101,8 @@ def lib() -> C.CDLL:
     sig("tcl_ipc_close", i32, [vp])
     sig("tcl_enable_peer", i32, [i32])
     sig("tcl_can_access_peer", i32, [i32, i32])
+    sig("tcl_memcpy_peer_async", i32, [vp, i32, vp, i32, C.c_size_t, vp])
+    sig("tcl_memcpy_async", i32, [vp, vp, C.c_size_t, vp])
     sig("tcl_vmm_granularity", i32, [i32, C.POINTER(C.c_size_t), i32, i32])
     sig("tcl_multicast_supported", i32, [i32])
     sig("tcl_vmm_create", i32, [i32, C.c_size_t, C.c_size_t, C.POINTER(u64), C.POINTER(i32), C.POINTER(vp)])

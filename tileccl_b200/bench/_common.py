@@ -62,6 +62,34 @@ def timed_series(fn, iters: int, warmup: int, before=None, flush=None) -> list[f
     return [a.elapsed_time(b) * 1e3 for a, b in zip(s, e)]
 
 
+def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=None) -> dict:
+    """Like :func:`timed_series` for several variants at once, taking one
+    iteration of each in turn, so that all of them see the same clocks and
+    temperature (the paired-baseline discipline of the reference,
+    comm_comp/exp1_ce_interference.cu:545-548)."""
+    names = list(fns)
+    for _ in range(warmup):
+        for n in names:
+            if before:
+                before()
+            fns[n]()
+    torch.cuda.synchronize()
+    G.host_barrier()
+    ev = {n: ([torch.cuda.Event(enable_timing=True) for _ in range(iters)],
+              [torch.cuda.Event(enable_timing=True) for _ in range(iters)]) for n in names}
+    for i in range(iters):
+        for n in names:
+            if flush:
+                flush()
+            if before:
+                before()
+            ev[n][0][i].record()
+            fns[n]()
+            ev[n][1][i].record()
+    torch.cuda.synchronize()
+    return {n: [a.elapsed_time(b) * 1e3 for a, b in zip(*ev[n])] for n in names}
+
+
 def stats_of(series):
     return make_stats(series)
 

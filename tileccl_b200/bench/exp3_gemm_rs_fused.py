@@ -85,9 +85,8 @@ def main(argv=None) -> int:
     if ctrl is not None:
         runners["ctrl"] = lambda: ctrl()
     order = [o for o in C.split_csv(args.order) if o in runners]
-    series = {}
-    for name in order:
-        series[name] = C.timed_series(runners[name], args.iters, args.warmup, before=bar, flush=flush)
+    # One iteration of every variant in turn, so that all see the same clocks.
+    series = C.timed_interleaved({n: runners[n] for n in order}, args.iters, args.warmup, before=bar, flush=flush)
     torch.cuda.synchronize()
     bar.check()
     fused.check()

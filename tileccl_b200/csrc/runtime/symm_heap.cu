@@ -104,6 +104,15 @@ int tcl_can_access_peer(int dev, int peer) {
   return ok;
 }
 
+// Copy-engine transport (the measured alternative to in-kernel ld/st): one
+// asynchronous peer copy.  src/dst may be IPC or VMM mappings of peer memory.
+int tcl_memcpy_peer_async(void* dst, int dst_dev, const void* src, int src_dev, size_t bytes, void* stream) {
+  return static_cast<int>(cudaMemcpyPeerAsync(dst, dst_dev, src, src_dev, bytes, static_cast<cudaStream_t>(stream)));
+}
+int tcl_memcpy_async(void* dst, const void* src, size_t bytes, void* stream) {
+  return static_cast<int>(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+}
+
 // ---- VMM back end -------------------------------------------------------------
 // Rounds `bytes` up to the allocation granularity of device `dev`.
 int tcl_vmm_granularity(int dev, size_t* gran, int multicast, int world) {
