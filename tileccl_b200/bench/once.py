@@ -1,0 +1,68 @@
+"""Single-GPU "once" runner: launches one kernel a few times and exits, for
+profiling with ncu (small case, few launches).
+
+    python -m tileccl_b200.bench.once gemm --m 8192 --n 8192 --k 8192 --cta-group 2 --launches 3
+    python -m tileccl_b200.bench.once gemm_rs --m 8192 --n 8192 --k 1024      (world of one, staged path)
+    python -m tileccl_b200.bench.once silu_mul --m 16384 --n 3584
+
+The reference's counterpart is ``peer_l2_probe --modes once`` (l2_peer_cache/peer_l2_probe.cu:53-58).
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+import torch
+
+from ..ops import elementwise as ew
+from ..ops.gemm import GemmPlan
+from ..ops.gemm_rs import GemmRs
+from ..parallel.heap import SymmetricHeap
+from . import _common as C
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("what", choices=["gemm", "gemm_rs", "silu_mul"])
+    ap.add_argument("--m", type=C.parse_size, default=8192)
+    ap.add_argument("--n", type=C.parse_size, default=8192)
+    ap.add_argument("--k", type=C.parse_size, default=8192)
+    ap.add_argument("--cta-group", type=int, default=2)
+    ap.add_argument("--launches", type=int, default=3)
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    M, N, K = args.m, args.n, args.k
+    if args.what == "silu_mul":
+        gu = torch.empty(M, 2 * N, dtype=torch.bfloat16, device=dev)
+        ew.fill_normal_(gu, seed=1)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        run = lambda: ew.silu_mul(gu, out)
+        check = lambda: None
+    else:
+        A = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+        Bt = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
+        ew.fill_normal_(A, seed=1)
+        ew.fill_normal_(Bt, seed=2)
+        if args.what == "gemm":
+            plan = GemmPlan(A, Bt, cta_group=args.cta_group)
+            run, check = plan, plan.check
+        else:
+            heap = SymmetricHeap(2 * M * N * 2 + (64 << 20))
+            op = GemmRs(heap, A, Bt, cta_group=args.cta_group, force_staged=True)
+            run, check = op, op.check
+    s = torch.cuda.Event(enable_timing=True)
+    e = torch.cuda.Event(enable_timing=True)
+    run()
+    torch.cuda.synchronize()
+    s.record()
+    for _ in range(args.launches):
+        run()
+    e.record()
+    torch.cuda.synchronize()
+    check()
+    print(f"{args.what} {M}x{N}x{K}: {s.elapsed_time(e) * 1e3 / args.launches:.1f} us per launch")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

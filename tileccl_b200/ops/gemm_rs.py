@@ -27,7 +27,7 @@ def staging_bytes(M: int, N: int, world: int) -> int:
 class GemmRs:
     def __init__(self, heap: SymmetricHeap, A: torch.Tensor, Bt: torch.Tensor, cta_group: int = 2,
                  rs_chunks: int = 0, comm_enabled: bool = True, group_m: int = 0, num_ctas: int = 0,
-                 timeout_ms: float = 4000.0, ablate: int = 0):
+                 timeout_ms: float = 4000.0, ablate: int = 0, force_staged: bool = False):
         require_bf16_rowmajor(A, "A")
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
@@ -52,7 +52,7 @@ class GemmRs:
         d.A, d.B = A.data_ptr(), Bt.data_ptr()
         d.world, d.rank = world, rank
         d.seg_rows = seg
-        if world == 1 and comm_enabled:
+        if world == 1 and comm_enabled and not force_staged:
             # One rank: nothing to reduce, the epilogue writes the result itself.
             comm_enabled = False
             self._direct = True
