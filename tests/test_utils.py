@@ -1,0 +1,67 @@
+"""Host-side helpers: size/shape parsing, statistics, CSV layout, roofline arithmetic, clocks."""
+import os
+
+import pytest
+
+from tileccl_b200.bench import _common as C
+from tileccl_b200.utils import clocks, csvio, roofline, stats
+
+
+def test_parse_size_and_shape():
+    assert C.parse_size("4096") == 4096 and C.parse_size("4K") == 4096 and C.parse_size("1.5M") == 1572864 and C.parse_size("1G") == 1 << 30
+    assert C.parse_shape("8192") == (8192, 8192, 8192)
+    assert C.parse_shape("32768x8192x1024") == (32768, 8192, 1024)
+    with pytest.raises(Exception):
+        C.parse_shape("1x2")
+    assert C.split_csv("a, b,,c") == ["a", "b", "c"]
+
+
+def test_stats_order_statistics():
+    s = stats.make_stats([5, 1, 4, 2, 3])
+    assert (s.n, s.min, s.max, s.p50, s.mean) == (5, 1, 5, 3, 3)
+    v = list(range(100))
+    s = stats.make_stats(v)
+    assert s.p95 == 95 and s.p99 == 99
+    assert stats.iters_for_ms(100.0, 10.0) == 100 and stats.iters_for_ms(0, 10) == 5
+
+
+def test_csv_headers_match_reference_layout():
+    assert csvio.EXP3_FUSED_COLUMNS[:27] == ("m,n,k,world,rank,base_us,base_p95,ctrl_us,ctrl_p95,fused_us,fused_p95,struct_sd,comm_sd,total_sd,"
+                                             "pull_gbps,max_rel_diff,base_p50,ctrl_p50,fused_p50,base_min,ctrl_min,fused_min,comm_sd_p50,"
+                                             "comm_sd_skew,comm_abs_us,order,iters").split(",")
+    assert csvio.EXP3_FUSED_COLUMNS[27:] == csvio.EXTRA_COLUMNS
+    assert csvio.SIGNAL_FANIN_COLUMNS == "mode,fanin,bytes,min_us,p50_us,p95_us,p99_us,verify".split(",")
+    assert csvio.EXP2_COLUMNS[:4] == ["m", "n", "k", "world"] and "seg_eff" in csvio.EXP2_COLUMNS
+
+
+def test_csv_append_and_multi_header_read(tmp_path):
+    p = str(tmp_path / "x.csv")
+    for run in range(2):
+        w = csvio.CsvAppender(p, ["m", "n", "order", "v"])
+        w.row(m=1 + run, n=2, order="a,b", v=3.14159)
+        w.close()
+    rows = csvio.read_rows(p)
+    assert len(rows) == 2 and rows[1]["m"] == "2" and rows[0]["order"] == "a|b" and rows[0]["v"] == "3.1416"
+    assert open(p).read().count("m,n,order,v") == 2
+
+
+def test_roofline_headline_shapes():
+    r = roofline.gemm_rs_roofline_us(32768, 8192, 1024, 8)
+    assert r["link_us"] == pytest.approx(7 / 8 * 32768 * 8192 * 2 / 770e9 * 1e6)
+    assert r["roofline_us"] == max(r["link_us"], r["compute_us"])
+    a = roofline.ag_gemm_roofline_us(32768, 3584, 8192, 8)
+    assert a["roofline_us"] == a["compute_us"] > a["link_us"]
+    assert roofline.gemm_rs_roofline_us(1024, 1024, 1024, 1)["link_us"] == 0
+
+
+def test_clock_summary_flags_throttling():
+    text = "\n".join([
+        "0, 1965, 1965, 250.0, 0x0, Not Active, Not Active, Not Active, Not Active",
+        "0, 1400, 1965, 990.0, 0x4, Not Active, Not Active, Not Active, Active",
+        "0, 1380, 1965, 1001.0, 0x4, Not Active, Not Active, Not Active, Active",
+        "0, 1200, 1965, 980.0, 0x8, Not Active, Active, Not Active, Not Active",
+    ])
+    s = clocks.summarize(clocks.parse_samples(text))
+    assert s["samples"] == 4 and s["sm_max_mhz"] == 1965 and s["sm_mhz"] in (1380.0, 1400.0)
+    assert "sw_power_cap" in s["reasons"] and "hw_thermal_slowdown" in s["reasons"]
+    assert clocks.summarize([])["sm_mhz"] is None

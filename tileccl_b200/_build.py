@@ -47,8 +47,7 @@ PROGRAMS: dict[str, tuple[list[str], list[str]]] = {
     "interference_matrix": (["bench/interference_matrix.cu"], []),
     "intra_sm_matrix": (["bench/intra_sm_matrix.cu"], []),
     "ce_gemm_overlap": (["bench/ce_gemm_overlap.cu"], ["-lcublas"]),
-    "exp1_ce_interference": (["bench/exp1_ce_interference.cu"], []),
-    "exp3_epilogue_remote": (["bench/exp3_epilogue_remote.cu"], []),
+    "exp1_ce_interference": (["bench/exp1_ce_interference.cu"], ["-L", str(LIB_DIR), "-ltileccl", "-Xlinker", "-rpath=$ORIGIN/../lib"]),
     "launcher_selftest": (["bench/launcher_selftest.cpp", "runtime/launcher.cpp"], []),
 }
 
