@@ -39,8 +39,8 @@ struct ProbeCtx {
     dev = device;
     TCL_CUDA_CHECK(cudaSetDevice(dev));
     TCL_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    TCL_CUDA_CHECK(cudaHostAlloc(const_cast<int**>(&stop_h), 4, cudaHostAllocMapped));
-    TCL_CUDA_CHECK(cudaHostGetDevicePointer(&stop_d, const_cast<int*>(stop_h), 0));
+    TCL_CUDA_CHECK(cudaHostAlloc(const_cast<int**>(&stop_h), 4, cudaHostAllocDefault));
+    TCL_CUDA_CHECK(cudaMalloc(&stop_d, 4));
     // Counters live in device memory (a probe writing host memory every iteration would load
     // PCIe and slow the host's own submissions); the host snapshots them with an async copy on
     // its own stream while the probe runs.
@@ -68,7 +68,7 @@ struct ProbeCtx {
   void launch(int kind, int nblocks, double max_ms, int l2_bytes) {
     TCL_CUDA_CHECK(cudaSetDevice(dev));
     blocks = std::min(nblocks, 1024);
-    *stop_h = 0;
+    TCL_CUDA_CHECK(cudaMemsetAsync(stop_d, 0, 4, st));
     TCL_CUDA_CHECK(cudaMemsetAsync(cnt_d, 0, 1024 * 8, st));
     // The host clock cannot be compared with %globaltimer: pass a relative budget, which
     // launch_kernel turns into an absolute device-clock deadline.
@@ -89,6 +89,8 @@ struct ProbeCtx {
   void stop() {
     *stop_h = 1;
     TCL_CUDA_CHECK(cudaSetDevice(dev));
+    TCL_CUDA_CHECK(cudaMemcpyAsync(stop_d, const_cast<int*>(stop_h), 4, cudaMemcpyHostToDevice, snap));
+    TCL_CUDA_CHECK(cudaStreamSynchronize(snap));
     TCL_CUDA_CHECK(cudaStreamSynchronize(st));
   }
   unsigned long long total() {

@@ -215,14 +215,18 @@ int main(int argc, char** argv) {
   if (tma_ok) TCL_CUDA_CHECK(cudaFuncSetAttribute(fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dyn_smem)));
 
   FusedArgs fa{};
+  // Stop flag and counters live in device memory; the host raises / snapshots them with async
+  // copies on its own stream, so the kernel's polling and counting never crosses PCIe.
   int* stop_h;
   unsigned long long* cnt_h;
-  TCL_CUDA_CHECK(cudaHostAlloc(&stop_h, 4, cudaHostAllocMapped));
-  TCL_CUDA_CHECK(cudaHostAlloc(&cnt_h, 64, cudaHostAllocMapped));
+  TCL_CUDA_CHECK(cudaHostAlloc(&stop_h, 4, cudaHostAllocDefault));
+  TCL_CUDA_CHECK(cudaHostAlloc(&cnt_h, 64, cudaHostAllocDefault));
   int* stop_d;
   unsigned long long* cnt_d;
-  TCL_CUDA_CHECK(cudaHostGetDevicePointer(&stop_d, stop_h, 0));
-  TCL_CUDA_CHECK(cudaHostGetDevicePointer(&cnt_d, cnt_h, 0));
+  TCL_CUDA_CHECK(cudaMalloc(&stop_d, 4));
+  TCL_CUDA_CHECK(cudaMalloc(&cnt_d, 64));
+  cudaStream_t snap;
+  TCL_CUDA_CHECK(cudaStreamCreateWithFlags(&snap, cudaStreamNonBlocking));
   fa.stop = stop_d;
   fa.comp_comm = cnt_d; fa.comp_pure = cnt_d + 1; fa.comm_bytes = cnt_d + 2;
   char *cs, *cd;
@@ -242,18 +246,26 @@ int main(int argc, char** argv) {
   auto run = [&](int probe, int comm, int cw) {
     fa.probe = probe; fa.comm = comm; fa.comm_warps = cw;
     fa.budget_ns = static_cast<unsigned long long>(window_ms + 2000) * 1000000ull;
-    *stop_h = 0;
-    cnt_h[0] = cnt_h[1] = cnt_h[2] = 0;
+    TCL_CUDA_CHECK(cudaMemsetAsync(stop_d, 0, 4, st));
+    TCL_CUDA_CHECK(cudaMemsetAsync(cnt_d, 0, 64, st));
+    auto snapshot = [&]() {
+      TCL_CUDA_CHECK(cudaMemcpyAsync(cnt_h, cnt_d, 24, cudaMemcpyDeviceToHost, snap));
+      TCL_CUDA_CHECK(cudaStreamSynchronize(snap));
+    };
     fused_kernel<<<blocks, warps * 32, comm == kCommTma ? dyn_smem : 0, st>>>(fa);
     TCL_CUDA_CHECK(cudaGetLastError());
     std::this_thread::sleep_for(std::chrono::milliseconds(30));
     volatile unsigned long long* c = cnt_h;
+    snapshot();
     const unsigned long long a0 = c[0], p0 = c[1], b0 = c[2];
     const double t0 = now_ms();
     std::this_thread::sleep_for(std::chrono::milliseconds(window_ms));
+    snapshot();
     const unsigned long long a1 = c[0], p1 = c[1], b1 = c[2];
     const double dt = (now_ms() - t0) / 1000.0;
     *stop_h = 1;
+    TCL_CUDA_CHECK(cudaMemcpyAsync(stop_d, stop_h, 4, cudaMemcpyHostToDevice, snap));
+    TCL_CUDA_CHECK(cudaStreamSynchronize(snap));
     TCL_CUDA_CHECK(cudaStreamSynchronize(st));
     RunOut o;
     o.comp_comm = (a1 - a0) / dt;

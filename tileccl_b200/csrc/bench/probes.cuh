@@ -31,7 +31,7 @@ inline const char* probe_unit(int k) {
 }
 
 struct ProbeArgs {
-  volatile int* stop;             // host-mapped: != 0 ends the probe
+  volatile int* stop;             // device memory: != 0 ends the probe
   unsigned long long* counters;   // device memory, one per CTA: iterations done (the host snapshots it)
   unsigned long long deadline_ns; // %globaltimer value after which the probe ends on its own
   uint4* buf;                     // hbm / l2 working set
@@ -39,6 +39,8 @@ struct ProbeArgs {
   float* sink;
 };
 
+// The stop flag is in device memory (the host raises it with an async copy): polling it costs an
+// L2 hit, not a PCIe read per warp.
 __device__ __forceinline__ bool probe_should_stop(const ProbeArgs& a) {
   return *a.stop != 0 || ptx::globaltimer_ns() > a.deadline_ns;
 }
