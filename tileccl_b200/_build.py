@@ -33,7 +33,7 @@ LIB_NAME = "libtileccl.so"
 LIB_SOURCES = [
     "ops/tileccl_ops.cu",
     "runtime/symm_heap.cu",
-    "ops/probe_kernels.cu",
+    "ops/no_alloc.cu",
 ]
 
 # Stand-alone programs: name -> (sources, extra link flags).
