@@ -1,0 +1,78 @@
+"""Verdict reducers of the analysis script, on synthetic bundles."""
+import os
+
+from tileccl_b200.bench import analyze, run_all
+from tileccl_b200.utils import csvio
+
+
+def _fused_row(w, **kv):
+    base = dict(m=8192, n=8192, k=1024, world=2, rank=0, base_us=100, base_p95=101, ctrl_us=102, ctrl_p95=103, fused_us=110, fused_p95=112,
+                base_p50=100, ctrl_p50=102, fused_p50=110, order="base|ctrl|fused", iters=10, nccl_cublas_us=150, roofline_us=90)
+    base.update(kv)
+    w.row(**base)
+
+
+def test_msweep_plateau_and_shift(tmp_path):
+    w = csvio.CsvAppender(str(tmp_path / "exp3_fused_msweep.csv"), csvio.EXP3_FUSED_COLUMNS)
+    for m in (4096, 8192, 16384, 32768):
+        tiles = (m // 128) * 32
+        for rank in (0, 1):
+            _fused_row(w, m=m, rank=rank, base_us=m / 10, ctrl_us=m / 10 * 1.02, fused_us=m / 10 * 1.02 + tiles * 0.08,
+                       base_p50=m / 10, ctrl_p50=m / 10 * 1.02, fused_p50=m / 10 * 1.02 + tiles * 0.08)
+    w.close()
+    txt = analyze.report(str(tmp_path))
+    assert "PLATEAU" in txt and "NO PLATEAU" not in txt
+    assert "SHIFT" in txt and "80.0" in txt          # 0.08 us per tile = 80 ns
+
+
+def test_tail_verdict_and_tail_shape(tmp_path):
+    w = csvio.CsvAppender(str(tmp_path / "exp3_fused_msweep.csv"), csvio.EXP3_FUSED_COLUMNS)
+    _fused_row(w, fused_us=130, fused_p50=104)        # the mean is lifted by outliers
+    _fused_row(w, rank=1, fused_us=130, fused_p50=104)
+    w.close()
+    d = csvio.CsvAppender(str(tmp_path / "iters_m8192.rank0.csv"), csvio.EXP3_ITER_COLUMNS)
+    for i in range(40):
+        d.row(m=8192, n=8192, k=1024, world=2, rank=0, variant="fused", iter=i, us=300.0 if i in (7, 23) else 100.0)
+    d.close()
+    txt = analyze.report(str(tmp_path))
+    assert "TAIL" in txt and "ISOLATED outliers" in txt
+
+
+def test_tiles_or_duration_and_order(tmp_path):
+    w = csvio.CsvAppender(str(tmp_path / "exp3_fused_ksweep.csv"), csvio.EXP3_FUSED_COLUMNS)
+    for k, ctrl in ((512, 50), (2048, 200), (8192, 800)):
+        _fused_row(w, k=k, ctrl_us=ctrl, fused_us=ctrl + 40, world=1)
+    w.close()
+    w = csvio.CsvAppender(str(tmp_path / "exp3_order.csv"), csvio.EXP3_FUSED_COLUMNS)
+    _fused_row(w, order="base|ctrl|fused", world=1)
+    _fused_row(w, order="fused|ctrl|base", world=1, ctrl_us=102.5)
+    w.close()
+    txt = analyze.report(str(tmp_path))
+    assert "TILES" in txt and "NO BIAS" in txt
+
+
+def test_l2_verdicts(tmp_path):
+    def write(tag, local, peer):
+        w = csvio.CsvAppender(str(tmp_path / f"{tag}_bw.csv"), csvio.PEER_L2_BW_COLUMNS)
+        for frac, g in local:
+            w.row(build="cg", target="local", bytes=int(frac * 1e8), frac_l2=frac, gbps=g)
+        for frac, g in peer:
+            w.row(build="cg", target="peer", bytes=int(frac * 1e8), frac_l2=frac, gbps=g)
+        w.close()
+    fr = (0.0625, 0.125, 0.25, 1.0, 2.0, 4.0)
+    write("probe_cg", [(f, 15000 if f < 1 else 6500) for f in fr], [(f, 760) for f in fr])
+    txt = analyze.report(str(tmp_path))
+    assert "NOT CACHED" in txt
+    write("probe_ca", [(f, 6500) for f in fr], [(f, 760) for f in fr])
+    assert "INCONCLUSIVE" in analyze.report(str(tmp_path))
+
+
+def test_manifest_resume_and_plan(tmp_path):
+    (tmp_path / "manifest.txt").write_text("a rc=0 seconds=1.0\nb rc=124 seconds=9.0\nc rc=0 seconds=2\nc rc=1 seconds=2\n")
+    assert run_all.done_steps(tmp_path) == {"a"}
+    names = [s[0] for s in run_all.plan(8, True, tmp_path)]
+    for want in ("exp3_fused_m32768", "exp2_ag_gemm", "exp1_ce_interference", "pk_bw_sweep", "signal_fanin", "sync_cost", "l2_probe_cg",
+                 "pipeline_e2e", "interference_matrix", "intra_sm_matrix", "ce_gemm_overlap", "mlp_e2e", "exp3_epilogue"):
+        assert want in names
+    assert len(set(names)) == len(names)
+    assert "2 not ok" in analyze.report(str(tmp_path))
