@@ -94,9 +94,12 @@ struct ProbeCtx {
     TCL_CUDA_CHECK(cudaStreamSynchronize(st));
   }
   unsigned long long total() {
+    int prev = 0;
+    TCL_CUDA_CHECK(cudaGetDevice(&prev));
     TCL_CUDA_CHECK(cudaSetDevice(dev));
     TCL_CUDA_CHECK(cudaMemcpyAsync(cnt_h, cnt_d, blocks * 8, cudaMemcpyDeviceToHost, snap));
     TCL_CUDA_CHECK(cudaStreamSynchronize(snap));
+    TCL_CUDA_CHECK(cudaSetDevice(prev));  // the caller may be driving the mover's device
     unsigned long long t = 0;
     for (int i = 0; i < blocks; ++i) t += cnt_h[i];
     return t;
