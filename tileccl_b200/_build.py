@@ -34,6 +34,7 @@ LIB_SOURCES = [
     "ops/tileccl_ops.cu",
     "runtime/symm_heap.cu",
     "ops/no_alloc.cu",
+    "ops/nvls_kernels.cu",
 ]
 
 # Stand-alone programs: name -> (sources, extra link flags).

@@ -112,6 +112,11 @@ def lib() -> C.CDLL:
     sig("tcl_mc_import", i32, [i32, C.POINTER(u64)])
     sig("tcl_mc_add_device", i32, [u64, i32])
     sig("tcl_mc_bind_and_map", i32, [u64, u64, C.c_size_t, C.c_size_t, i32, C.POINTER(vp)])
+    sig("tcl_mc_unbind", i32, [u64, i32, C.c_size_t])
+    sig("tcl_nvls_bcast", i32, [vp, vp, C.c_size_t, i32, vp])
+    sig("tcl_nvls_ld_reduce", i32, [vp, vp, C.c_size_t, i32, vp])
+    sig("tcl_nvls_red", i32, [vp, vp, C.c_size_t, i32, vp])
+    sig("tcl_p2p_copy", i32, [vp, vp, C.c_size_t, i32, vp])
     _lib = L
     return L
 

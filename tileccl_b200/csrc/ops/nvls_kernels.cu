@@ -1,0 +1,72 @@
+// NVLS (NVLink SHARP) data movers: multimem instructions on a multicast mapping of the symmetric heap.
+//   bcast      local -> every GPU        multimem.st            (the all-gather building block)
+//   ld_reduce  every GPU -> local sum    multimem.ld_reduce     (the reduce-scatter building block; the
+//                                                                switch adds the bf16 values in fp32)
+//   red        local -> added everywhere multimem.red
+// and a plain peer copy (ld/st through a peer mapping) for comparison.  Simple grid-stride kernels: they
+// are the movers of the NVLS bandwidth sweep, and the in-switch reduce path of the fused GEMM+RS reuses
+// the same instruction wrappers (ptx/ldst_sys.cuh).
+//
+// The reference has no multicast path (no multimem anywhere in it).
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../ptx/ldst_sys.cuh"
+
+namespace {
+using namespace tcl::ptx;
+
+__global__ void nvls_bcast_kernel(uint4* mc_dst, const uint4* __restrict__ src, size_t nvec) {
+  const size_t st = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += st) multimem_st_v4(mc_dst + i, ld_v4_stream(src + i));
+}
+__global__ void nvls_ld_reduce_kernel(const uint4* mc_src, uint4* __restrict__ dst, size_t nvec) {
+  const size_t st = (size_t)gridDim.x * blockDim.x;
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  for (; i + 3 * st < nvec; i += 4 * st) {
+    const uint4 a = multimem_ld_reduce_bf16x8(mc_src + i), b = multimem_ld_reduce_bf16x8(mc_src + i + st);
+    const uint4 c = multimem_ld_reduce_bf16x8(mc_src + i + 2 * st), d = multimem_ld_reduce_bf16x8(mc_src + i + 3 * st);
+    st_v4(dst + i, a); st_v4(dst + i + st, b); st_v4(dst + i + 2 * st, c); st_v4(dst + i + 3 * st, d);
+  }
+  for (; i < nvec; i += st) st_v4(dst + i, multimem_ld_reduce_bf16x8(mc_src + i));
+}
+__global__ void nvls_red_kernel(uint4* mc_dst, const uint4* __restrict__ src, size_t nvec) {
+  const size_t st = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += st) multimem_red_bf16x8(mc_dst + i, ld_v4_stream(src + i));
+}
+__global__ void p2p_copy_kernel(uint4* dst, const uint4* __restrict__ src, size_t nvec) {
+  const size_t st = (size_t)gridDim.x * blockDim.x;
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  for (; i + 3 * st < nvec; i += 4 * st) {
+    const uint4 a = ld_v4_stream(src + i), b = ld_v4_stream(src + i + st), c = ld_v4_stream(src + i + 2 * st), d = ld_v4_stream(src + i + 3 * st);
+    st_v4(dst + i, a); st_v4(dst + i + st, b); st_v4(dst + i + 2 * st, c); st_v4(dst + i + 3 * st, d);
+  }
+  for (; i < nvec; i += st) st_v4(dst + i, ld_v4_stream(src + i));
+}
+
+int grid_for(size_t nvec, int blocks) {
+  if (blocks > 0) return blocks;
+  size_t b = (nvec + 1023) / 1024;
+  return static_cast<int>(b < 1 ? 1 : (b > 148 * 4 ? 148 * 4 : b));
+}
+}  // namespace
+
+extern "C" {
+int tcl_nvls_bcast(void* mc_dst, const void* src, size_t bytes, int blocks, void* stream) {
+  nvls_bcast_kernel<<<grid_for(bytes / 16, blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(mc_dst), static_cast<const uint4*>(src), bytes / 16);
+  return static_cast<int>(cudaGetLastError());
+}
+int tcl_nvls_ld_reduce(const void* mc_src, void* dst, size_t bytes, int blocks, void* stream) {
+  nvls_ld_reduce_kernel<<<grid_for(bytes / 16, blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(mc_src), static_cast<uint4*>(dst), bytes / 16);
+  return static_cast<int>(cudaGetLastError());
+}
+int tcl_nvls_red(void* mc_dst, const void* src, size_t bytes, int blocks, void* stream) {
+  nvls_red_kernel<<<grid_for(bytes / 16, blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(mc_dst), static_cast<const uint4*>(src), bytes / 16);
+  return static_cast<int>(cudaGetLastError());
+}
+int tcl_p2p_copy(void* dst, const void* src, size_t bytes, int blocks, void* stream) {
+  p2p_copy_kernel<<<grid_for(bytes / 16, blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(dst), static_cast<const uint4*>(src), bytes / 16);
+  return static_cast<int>(cudaGetLastError());
+}
+}

@@ -221,4 +221,10 @@ int tcl_mc_bind_and_map(uint64_t mc, uint64_t mem_handle, size_t bytes, size_t g
   return map_handle(static_cast<CUmemGenericAllocationHandle>(mc), bytes, gran, dev, mc_ptr);
 }
 
+// Before the physical memory is released: detach this device's memory from the multicast object.
+int tcl_mc_unbind(uint64_t mc, int dev, size_t bytes) {
+  DRV(cuMulticastUnbind);
+  return static_cast<int>(fn_cuMulticastUnbind(static_cast<CUmemGenericAllocationHandle>(mc), dev, 0, bytes));
+}
+
 }  // extern "C"

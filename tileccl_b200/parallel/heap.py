@@ -174,6 +174,7 @@ class SymmetricHeap:
             q = C.c_void_p()
             _native.check(self.lib.tcl_mc_bind_and_map(mc.value, self._local_handle, self.nbytes, g, self.device, C.byref(q)), "cuMulticastBindMem")
             self.mc_base = q.value
+            self._mc_handle = mc.value
             G.host_barrier(self.group)
 
     # ---- allocation ------------------------------------------------------------
@@ -236,3 +237,19 @@ class SymmetricHeap:
             if self.base[self.rank]:
                 self.lib.tcl_heap_free(C.c_void_p(self.base[self.rank]))
                 self.base[self.rank] = 0
+        elif self.backend == "vmm" and self.base[self.rank]:
+            # Order matters: nobody may lose its memory while a peer can still reach it through the
+            # multicast object or a peer mapping.  Every step is followed by a host barrier.
+            if self.mc_base is not None:
+                self.lib.tcl_mc_unbind(self._mc_handle, self.device, self.nbytes)
+                self.lib.tcl_vmm_unmap(C.c_void_p(self.mc_base), self.nbytes, self._mc_handle)
+                self.mc_base = None
+            G.host_barrier(self.group)
+            own = self._handles[0]
+            for r, h in zip([x for x in range(self.world) if x != self.rank], self._handles[1:]):
+                self.lib.tcl_vmm_unmap(C.c_void_p(self.base[r]), self.nbytes, h)
+                self.base[r] = 0
+            G.host_barrier(self.group)
+            self.lib.tcl_vmm_unmap(C.c_void_p(self.base[self.rank]), self.nbytes, own)
+            self.base[self.rank] = 0
+            self._handles = []
