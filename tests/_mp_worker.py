@@ -73,6 +73,7 @@ def main():
             excess = ((out.float() - ref[sl]).abs() - bound).max().item()
             if excess > 0:
                 fails.append(f"gemm_rs g{cta_group} iter {it}: error exceeds the bf16 rounding bound by {excess}")
+            op.audit()
             op.stage.fill_(float("nan"))
             torch.cuda.synchronize()
             dist.barrier()
@@ -95,7 +96,34 @@ def main():
                 e = rel(out, full.float() @ Bt.float().t())
                 if e > 2e-2 or not torch.equal(op.a_full, full):
                     fails.append(f"ag_gemm g{cta_group} rows {gather_rows} iter {it}: rel err {e}")
+                op.audit()
                 dist.barrier()
+
+    # ---- GEMM + reduce-scatter through the NVSwitch (multimem.ld_reduce), when multicast is available ----
+    from tileccl_b200 import _native
+    if _native.lib().tcl_multicast_supported(torch.cuda.current_device()):
+        mc_heap = SymmetricHeap(128 << 20, backend="vmm", multicast=True)
+        M, N, K = 512 * world, 512, 256
+        A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        op = GemmRs(mc_heap, A, Bt, cta_group=2, transport="nvls", timeout_ms=2000)
+        parts = [a.float() @ b.float().t() for a, b in zip(gather(A), gather(Bt))]
+        ref = sum(parts)
+        seg = M // world
+        sl = slice(rank * seg, (rank + 1) * seg)
+        # the switch's final conversion is allowed a whole bf16 ulp (2^-7), the partials half an ulp each
+        bound = 1.05 * (2.0 ** -8 * sum(p.abs() for p in parts) + 2.0 ** -7 * ref.abs())[sl] + 1e-2
+        for it in range(2):
+            out = op()
+            op.check()
+            excess = ((out.float() - ref[sl]).abs() - bound).max().item()
+            if excess > 0:
+                fails.append(f"gemm_rs nvls iter {it}: error exceeds the bf16 rounding bound by {excess}")
+            op.audit()
+            torch.cuda.synchronize()
+            dist.barrier()
+        del op
+        mc_heap.close()
 
     # ---- MLP block ----
     tokens, hidden, ffn = 512 * world, 512, 1024 * world

@@ -51,6 +51,7 @@ class GemmDesc(C.Structure):
         ("timeout_ns", C.c_uint64),
         ("group_m", C.c_int32),
         ("num_ctas", C.c_int32),
+        ("rs_mc_stage", C.c_void_p),
         ("ablate", C.c_int32),
     ]
 

@@ -49,6 +49,7 @@ def build_parser():
     ap.add_argument("--rs-chunks", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--ablate", type=int, default=0, help="timing-only knobs of the fused variant: 1 = no reduce warps, 2 = no tile signals, 3 = both")
+    ap.add_argument("--transport", default="p2p", choices=["p2p", "nvls"], help="p2p: epilogue pushes partial tiles to the owner; nvls: partials stay local, the owner pulls sums with multimem.ld_reduce")
     ap.add_argument("--verify", action="store_true")
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between iterations")
     ap.add_argument("--csv", default=None)
@@ -62,7 +63,8 @@ def main(argv=None) -> int:
     M, N = args.m, args.n
     K = args.k if args.k > 0 else args.k_global // world
     dev = torch.device("cuda", torch.cuda.current_device())
-    heap = SymmetricHeap(2 * (M * N * 2 + (M // world) * N * 2) + (64 << 20))
+    nvls = args.transport == "nvls" and world > 1
+    heap = SymmetricHeap(2 * (M * N * 2 + (M // world) * N * 2) + (64 << 20), backend="vmm" if nvls else "ipc", multicast=nvls)
     A = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
     Bt = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
     ew.fill_normal_(A, seed=1000 + rank)
@@ -70,7 +72,7 @@ def main(argv=None) -> int:
     D = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     plain = GemmPlan(A, Bt, out=D, cta_group=args.cta_group)
     fused = GemmRs(heap, A, Bt, cta_group=args.cta_group, rs_chunks=args.rs_chunks, group_m=args.group_m,
-                   ablate=args.ablate)
+                   ablate=args.ablate, transport=args.transport)
     ctrl = GemmRs(heap, A, Bt, cta_group=args.cta_group, rs_chunks=args.rs_chunks, group_m=args.group_m,
                   comm_enabled=False)
     bar = ew.DeviceBarrier(heap)
@@ -124,7 +126,7 @@ def main(argv=None) -> int:
         fused_max = max(r["f"].mean for r in allr)
         nccl_max = max(r["n"].mean for r in allr)
         print(f"# exp3 fused GEMM+RS  M={M} N={N} K/rank={K} world={world} cta_group={args.cta_group} "
-              f"rs_chunks={fused.plan.desc.rs_chunks} iters={args.iters}  [{C.device_line()}]")
+              f"transport={fused.transport} iters={args.iters}  [{C.device_line()}]")
         print("rank |  base us   TF/s |  ctrl us | fused us   TF/s | struct   comm  total | push GB/s | nccl+cublas us | verify")
         csv = csvio.CsvAppender(args.csv, csvio.EXP3_FUSED_COLUMNS)
         for r in allr:

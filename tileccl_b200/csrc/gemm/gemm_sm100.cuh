@@ -94,6 +94,9 @@ struct GemmParams {
   const __nv_bfloat16* rs_stage;      // this rank's staging [world][seg_rows][N]
   __nv_bfloat16* rs_out;              // this rank's reduced shard [seg_rows][ld_out]
   int ld_out;
+  // NVLS variant: partial tiles stay in the producer's own full-size staging [M][N]; the owner's reduce
+  // warps read this multicast address of it, and the NVSwitch returns the sum over all ranks.
+  const __nv_bfloat16* rs_mc_stage;   // multicast mapping of the staging buffer, or nullptr (P2P push)
 
   // AG+GEMM
   const __nv_bfloat16* ag_src[kMaxWorld];  // rank s's shard [seg_rows][K] (a peer pointer)
@@ -192,6 +195,21 @@ __device__ __forceinline__ void reduce_tile(const __nv_bfloat16* __restrict__ st
       o.w = ptx::pack_bf16x2(__float_as_uint(acc[6]), __float_as_uint(acc[7]));
       ptx::st_v4(out + out_off + static_cast<size_t>((pass + j) * 4 + r_base) * ld_out, o);
     }
+  }
+}
+
+// NVLS form of reduce_tile: one multimem.ld_reduce per 16 bytes returns the sum (fp32 accumulation in
+// the switch) of the same tile in every rank's staging buffer.  8 loads in flight per thread.
+__device__ __forceinline__ void reduce_tile_nvls(const __nv_bfloat16* mc_tile, int ldn, __nv_bfloat16* __restrict__ out,
+                                                 size_t out_off, int ld_out, int ctid) {
+  const int r_base = ctid >> 5;
+#pragma unroll 1
+  for (int pass = 0; pass < 32; pass += 8) {
+    uint4 w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[j] = ptx::multimem_ld_reduce_bf16x8(mc_tile + static_cast<size_t>((pass + j) * 4 + r_base) * ldn);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ptx::st_v4(out + out_off + static_cast<size_t>((pass + j) * 4 + r_base) * ld_out, w[j]);
   }
 }
 
@@ -513,6 +531,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int colc = ctid & 31;  // 16-byte column chunk of the 256-column tile
         const size_t tile_off = static_cast<size_t>(seg_row) * Cfg::BM * p.N + n_blk * Cfg::BN + colc * 8;
         const size_t out_off = static_cast<size_t>(seg_row) * Cfg::BM * p.ld_out + n_blk * Cfg::BN + colc * 8;
+        if (p.rs_mc_stage != nullptr) {
+          // this rank's segment starts at row rank * seg_rows of every rank's full-size staging
+          const size_t row0 = static_cast<size_t>(p.rank) * p.seg_rows + static_cast<size_t>(seg_row) * Cfg::BM;
+          detail::reduce_tile_nvls(p.rs_mc_stage + row0 * p.N + n_blk * Cfg::BN + colc * 8, p.N, p.rs_out, out_off, p.ld_out, ctid);
+          continue;
+        }
         switch (p.world) {
           case 1: detail::reduce_tile<1, 8>(p.rs_stage, slot_elems, tile_off, p.N, p.rs_out, out_off, p.ld_out, ctid, 1); break;
           case 2: detail::reduce_tile<2, 8>(p.rs_stage, slot_elems, tile_off, p.N, p.rs_out, out_off, p.ld_out, ctid, 2); break;

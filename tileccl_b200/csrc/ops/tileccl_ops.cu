@@ -275,6 +275,7 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
     p.rs_stage = static_cast<const __nv_bfloat16*>(d->rs_stage);
     p.rs_out = static_cast<__nv_bfloat16*>(d->rs_out);
     p.ld_out = d->ld_out;
+    p.rs_mc_stage = static_cast<const __nv_bfloat16*>(d->rs_mc_stage);
   } else if (d->mode == TCL_MODE_AG_GEMM) {
     if (nseg != d->world) return fail("AG+GEMM: M / seg_rows must equal world");
     if (d->lda != d->K) return fail("AG+GEMM: gathered A must be dense (lda == K)");

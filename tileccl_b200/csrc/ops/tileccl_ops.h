@@ -51,6 +51,7 @@ typedef struct tcl_gemm_desc {
   uint64_t timeout_ns;  /* bound of every device-side wait; 0 = 4 s */
   int32_t group_m;      /* raster group height; 0 = default */
   int32_t num_ctas;     /* 0 = one per SM */
+  const void* rs_mc_stage; /* GEMM+RS NVLS variant: multicast mapping of the [M][N] staging buffer, else NULL */
   int32_t ablate;       /* experiments only: bit 0 = no reduce warps, bit 1 = no tile signals */
 } tcl_gemm_desc;
 

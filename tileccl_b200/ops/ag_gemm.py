@@ -74,6 +74,24 @@ class AgGemm:
     def check(self) -> None:
         self.plan.check()
 
+    def audit(self) -> None:
+        """Flag audit after a run: every gathered row block of a peer segment stands at
+        epoch * (gather_rows / 8) arrivals, the local segment's flags were never touched, and all
+        peers reported that they finished reading this rank's shard.  Synchronises."""
+        h = self.heap
+        if h.world == 1 or not self.plan.desc.comm_enabled:
+            return
+        M = self.a_full.shape[0]
+        seg = M // h.world
+        per = self.gather_rows // 8 * self.plan.epoch
+        flags = self.flags[: M // self.gather_rows].tolist()
+        for b, v in enumerate(flags):
+            own = (b * self.gather_rows) // seg == h.rank
+            if v != (0 if own else per):
+                raise AssertionError(f"gather flag {b} is {v}, expected {0 if own else per}")
+        if int(self.done[16]) != self.plan.epoch * (h.world - 1):
+            raise AssertionError("not every peer reported the end of its reads")
+
     @property
     def launches(self) -> int:
         return self.plan.launches

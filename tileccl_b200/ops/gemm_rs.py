@@ -27,11 +27,17 @@ def staging_bytes(M: int, N: int, world: int) -> int:
 class GemmRs:
     def __init__(self, heap: SymmetricHeap, A: torch.Tensor, Bt: torch.Tensor, cta_group: int = 2,
                  rs_chunks: int = 0, comm_enabled: bool = True, group_m: int = 0, num_ctas: int = 0,
-                 timeout_ms: float = 4000.0, ablate: int = 0, force_staged: bool = False):
+                 timeout_ms: float = 4000.0, ablate: int = 0, force_staged: bool = False, transport: str = "p2p"):
         require_bf16_rowmajor(A, "A")
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
         world, rank = heap.world, heap.rank
+        if transport not in ("p2p", "nvls"):
+            raise ValueError("transport must be 'p2p' or 'nvls'")
+        nvls = transport == "nvls" and world > 1 and comm_enabled
+        if nvls and heap.mc_base is None:
+            raise ValueError("transport='nvls' needs a heap with a multicast mapping (backend='vmm', multicast=True)")
+        self.transport = "nvls" if nvls else "p2p"
         M, K = A.shape
         N = Bt.shape[0]
         if M % world:
@@ -63,6 +69,10 @@ class GemmRs:
             if self._direct:
                 d.dst_base[s] = self.out.data_ptr()
                 d.dst_row_off[s] = 0
+            elif nvls:
+                # NVLS: partial tiles stay in this rank's own staging at their global row; owners pull sums
+                d.dst_base[s] = self.stage.data_ptr()
+                d.dst_row_off[s] = s * seg
             elif comm_enabled:
                 # Segment s goes to rank s's staging, slot `rank`.
                 d.dst_base[s] = heap.peer_ptr(self.stage, s)
@@ -77,6 +87,7 @@ class GemmRs:
         d.rs_out = self.out.data_ptr()
         d.ld_out = N
         d.rs_chunks = rs_chunks
+        d.rs_mc_stage = heap.mc_ptr(self.stage) if nvls else None
         d.timeout_ns = int(timeout_ms * 1e6)
         d.group_m, d.num_ctas = group_m, num_ctas
         d.ablate = ablate
@@ -89,6 +100,17 @@ class GemmRs:
 
     def check(self) -> None:
         self.plan.check()
+
+    def audit(self) -> None:
+        """Flag audit after a run: every per-tile counter of this rank stands at epoch * world (each
+        producer signalled each tile exactly once per call).  Synchronises."""
+        if self._direct or not self.plan.desc.comm_enabled or self.plan.desc.ablate:
+            return
+        want = self.plan.epoch * self.heap.world
+        bad = (self.tile_cnt != want).nonzero()
+        if bad.numel():
+            i = int(bad[0])
+            raise AssertionError(f"tile counter {i} is {int(self.tile_cnt[i])}, expected {want}")
 
     @property
     def launches(self) -> int:
