@@ -21,7 +21,7 @@
 //   warp 0      TMA producer (one lane)
 //   warp 1      TMEM allocation + tcgen05.mma issue (one lane, leader CTA only)
 //   warps 2-5   epilogue: tcgen05.ld -> bf16 -> swizzled smem transpose ->
-//               coalesced 16-byte global stores (local or peer)
+//               coalesced 16-byte global stores, 256 contiguous bytes per row (local or peer)
 //   warps 6-9   communication: reduce warps (GEMM+RS) or gather warps (AG+GEMM)
 //   warp 10     GEMM+RS signalling: publishes finished tiles to their owners
 //
@@ -127,8 +127,8 @@ struct GemmCfg {
   static constexpr int STAGES = (kCtaGroup == 1) ? 4 : 6;
   static constexpr int EPI_WARPS = 4;
   static constexpr int EPI_CHUNK_COLS = 64;         // bf16 columns per transpose chunk
-  static constexpr int EPI_BUF_BYTES = 32 * EPI_CHUNK_COLS * 2;   // 4 KiB
-  static constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES; // double buffered
+  static constexpr int EPI_BUF_BYTES = 32 * 2 * EPI_CHUNK_COLS * 2;   // 8 KiB: 32 rows x 128 columns per warp
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUF_BYTES;
   static constexpr int COMM_WARPS = 4;
   static constexpr int SIGNAL_WARP = 2 + EPI_WARPS + COMM_WARPS;  // index of the signalling warp
   static constexpr int THREADS = (3 + EPI_WARPS + COMM_WARPS) * 32;
@@ -399,7 +399,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ===== epilogue =====
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int ew = warp - 2;
-    const uint32_t my_buf = epi_u32 + ew * 2 * Cfg::EPI_BUF_BYTES;
+    const uint32_t my_buf = epi_u32 + ew * Cfg::EPI_BUF_BYTES;
     bool ok = true;
     bool barrier_passed = !(fused_comm && p.mode == kModeGemmRs);
     int lt = 0;
@@ -458,10 +458,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
             else mbar_arrive_cluster(mapa(bar_tempty + 8 * b, 0));
           }
         }
-        // Row `lane` of this warp's 32 rows, 64 columns -> 8 chunks of 16 bytes,
-        // chunk j stored at slot j ^ (lane & 7) so that both the row-wise
-        // writes and the transposed reads are bank-conflict free.
-        const uint32_t buf = my_buf + (c & 1) * Cfg::EPI_BUF_BYTES;
+        // The warp's buffer holds 32 rows x 128 columns (256 bytes per row), filled by two
+        // 64-column TMEM reads.  Row `lane`, 16-byte slot k is stored at slot k ^ (lane & 7):
+        // the row-wise writes and the transposed reads are both bank-conflict free.
+        const int half = c & 1;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 w;
@@ -469,7 +469,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           w.y = pack_bf16x2(v0[8 * j + 2], v0[8 * j + 3]);
           w.z = pack_bf16x2(v0[8 * j + 4], v0[8 * j + 5]);
           w.w = pack_bf16x2(v0[8 * j + 6], v0[8 * j + 7]);
-          sts_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), w);
+          sts_v4(my_buf + lane * 256 + (((half * 8 + j) ^ (lane & 7)) << 4), w);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -478,21 +478,23 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           w.y = pack_bf16x2(v1[8 * j + 2], v1[8 * j + 3]);
           w.z = pack_bf16x2(v1[8 * j + 4], v1[8 * j + 5]);
           w.w = pack_bf16x2(v1[8 * j + 6], v1[8 * j + 7]);
-          sts_v4(buf + lane * 128 + (((j + 4) ^ (lane & 7)) << 4), w);
+          sts_v4(my_buf + lane * 256 + (((half * 8 + j + 4) ^ (lane & 7)) << 4), w);
         }
+        if (half == 0) continue;
         __syncwarp();
-        // 8 lanes cover one row's 128 contiguous bytes; 4 rows per instruction.
-        const int ch = lane & 7;
-        const int gcol = col0 + c * Cfg::EPI_CHUNK_COLS + ch * 8;
+        // 16 lanes cover one row's 256 contiguous bytes; 2 rows per store instruction.
+        const int ch = lane & 15;
+        const int ccol = (c - 1) * Cfg::EPI_CHUNK_COLS + ch * 8;   // column inside the tile
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int r = i * 4 + (lane >> 3);
-          const uint4 w = lds_v4(buf + r * 128 + ((ch ^ (r & 7)) << 4));
+        for (int i = 0; i < 16; ++i) {
+          const int r = i * 2 + (lane >> 4);
+          const uint4 w = lds_v4(my_buf + r * 256 + ((ch ^ (r & 7)) << 4));
           const int grow = row0 + q * 32 + r;
-          if (grow < p.M && gcol < p.N) {
-            st_v4(dst0 + static_cast<long long>(q * 32 + r) * p.ldc + c * Cfg::EPI_CHUNK_COLS + ch * 8, w);
+          if (grow < p.M && col0 + ccol < p.N) {
+            st_v4(dst0 + static_cast<long long>(q * 32 + r) * p.ldc + ccol, w);
           }
         }
+        __syncwarp();   // the buffer is rewritten by the next pair of reads
       }
       if (p.mode == kModeGemmRs && p.comm_enabled) {
         // This warp's 32 rows of the tile are stored.  Publishing them needs a
@@ -570,14 +572,39 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const char* src = reinterpret_cast<const char*>(p.ag_src[seg] + row_in_seg * p.K);
           const size_t grow = static_cast<size_t>(seg) * p.seg_rows + row_in_seg;
           char* dst = reinterpret_cast<char*>(p.ag_full + grow * p.K);
+          // Two register banks of 8 x 16 bytes per lane: the loads of one 4 KiB step are issued
+          // before the previous step is stored, so 8 to 16 peer loads per lane are always in flight.
           constexpr int kUnroll = 8;
+          constexpr size_t kStep = kUnroll * 512;
           size_t off = static_cast<size_t>(lane) * 16;
-          for (; off + (kUnroll - 1) * 512 < item_bytes; off += kUnroll * 512) {
-            uint4 w[kUnroll];
+          auto fits = [&](size_t o) { return o + (kUnroll - 1) * 512 < item_bytes; };
+          if (fits(off)) {
+            uint4 wa[kUnroll], wb[kUnroll];
 #pragma unroll
-            for (int u = 0; u < kUnroll; ++u) w[u] = ld_v4_stream(src + off + u * 512);
+            for (int u = 0; u < kUnroll; ++u) wa[u] = ld_v4_stream(src + off + u * 512);
+            size_t nxt = off + kStep;
+            for (;;) {
+              bool more = fits(nxt);
+              if (more) {
 #pragma unroll
-            for (int u = 0; u < kUnroll; ++u) st_v4(dst + off + u * 512, w[u]);
+                for (int u = 0; u < kUnroll; ++u) wb[u] = ld_v4_stream(src + nxt + u * 512);
+              }
+#pragma unroll
+              for (int u = 0; u < kUnroll; ++u) st_v4(dst + off + u * 512, wa[u]);
+              off = nxt;
+              nxt += kStep;
+              if (!more) break;
+              more = fits(nxt);
+              if (more) {
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) wa[u] = ld_v4_stream(src + nxt + u * 512);
+              }
+#pragma unroll
+              for (int u = 0; u < kUnroll; ++u) st_v4(dst + off + u * 512, wb[u]);
+              off = nxt;
+              nxt += kStep;
+              if (!more) break;
+            }
           }
           for (; off < item_bytes; off += 512) st_v4(dst + off, ld_v4_stream(src + off));
           // The consumer of these rows is TMA (async proxy) on another SM.
