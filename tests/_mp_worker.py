@@ -81,8 +81,8 @@ def main():
         # ---- fused all-gather + GEMM ----
         M, N, K = 256 * cta_group * world, 768, 512
         Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
-        for gather_rows in (128, 256 * cta_group):
-            op = AgGemm(heap, M, K, Bt, cta_group=cta_group, gather_rows=gather_rows, timeout_ms=2000)
+        for gather_rows, transport in ((128, "push"), (256 * cta_group, "push"), (256 * cta_group, "pull")):
+            op = AgGemm(heap, M, K, Bt, cta_group=cta_group, gather_rows=gather_rows, timeout_ms=2000, transport=transport)
             for it in range(3):
                 shard = torch.randn(M // world, K, device="cuda", dtype=torch.bfloat16)
                 # poison the peers' part of the gathered buffer: stale rows must not be used
@@ -95,7 +95,7 @@ def main():
                 full = torch.cat(gather(shard), 0)
                 e = rel(out, full.float() @ Bt.float().t())
                 if e > 2e-2 or not torch.equal(op.a_full, full):
-                    fails.append(f"ag_gemm g{cta_group} rows {gather_rows} iter {it}: rel err {e}")
+                    fails.append(f"ag_gemm {transport} g{cta_group} rows {gather_rows} iter {it}: rel err {e}")
                 op.audit()
                 dist.barrier()
 

@@ -19,7 +19,8 @@ def _tiles(lib, m_tiles, n_tiles, group_m, order, world, rank, chunks):
 
 @pytest.mark.parametrize("order,world,chunks", [
     (_native.ORDER_PLAIN, 1, 1), (_native.ORDER_RS_PUSH, 2, 2), (_native.ORDER_RS_PUSH, 8, 4),
-    (_native.ORDER_RS_PUSH, 3, 1), (_native.ORDER_AG_PULL, 4, 1), (_native.ORDER_AG_PULL, 7, 1)])
+    (_native.ORDER_RS_PUSH, 3, 1), (_native.ORDER_AG_PULL, 4, 1), (_native.ORDER_AG_PULL, 7, 1),
+    (_native.ORDER_AG_PUSH, 2, 1), (_native.ORDER_AG_PUSH, 8, 1), (_native.ORDER_AG_PUSH, 5, 1)])
 @pytest.mark.parametrize("group_m", [1, 3, 8])
 def test_schedule_is_a_bijection(native_lib, order, world, chunks, group_m):
     seg_tiles = 4 * chunks
@@ -69,3 +70,14 @@ def test_owner_and_counter_index():
     assert tiling.owner_of_row(row=4096 + 130, seg_rows=4096) == 1
     assert tiling.rs_counter_index(row=4096 + 256, col=512, seg_rows=4096, n_cols=8192) == 2 * 32 + 2
     assert tiling.gather_flag_index(row=5000, gather_rows=512) == 9
+
+
+def test_ag_push_order_follows_arrival():
+    world, seg_tiles = 4, 3
+    for r in range(world):
+        ms = [tiling.m_of_row(p, world * seg_tiles, _native.ORDER_AG_PUSH, world, r, 1) for p in range(world * seg_tiles)]
+        assert [m // seg_tiles for m in ms[:seg_tiles]] == [r] * seg_tiles          # own segment first
+        rest = ms[seg_tiles:]
+        # then tile row i of every peer before tile row i + 1 of any peer
+        assert [m % seg_tiles for m in rest] == [i for i in range(seg_tiles) for _ in range(world - 1)]
+        assert {m // seg_tiles for m in rest[:world - 1]} == set(range(world)) - {r}

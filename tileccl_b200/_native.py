@@ -11,7 +11,7 @@ from pathlib import Path
 
 MAX_WORLD = 8
 MODE_PLAIN, MODE_GEMM_RS, MODE_AG_GEMM = 0, 1, 2
-ORDER_PLAIN, ORDER_RS_PUSH, ORDER_AG_PULL = 0, 1, 2
+ORDER_PLAIN, ORDER_RS_PUSH, ORDER_AG_PULL, ORDER_AG_PUSH = 0, 1, 2, 3
 
 _LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtileccl.so"
 
@@ -46,6 +46,9 @@ class GemmDesc(C.Structure):
         ("gather_rows", C.c_int32),
         ("ag_done", C.c_void_p),
         ("ag_read_done", C.c_void_p * MAX_WORLD),
+        ("ag_push", C.c_int32),
+        ("ag_dst", C.c_void_p * MAX_WORLD),
+        ("ag_flag_peer", C.c_void_p * MAX_WORLD),
         ("barrier", C.c_void_p * MAX_WORLD),
         ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),

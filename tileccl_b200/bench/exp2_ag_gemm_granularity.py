@@ -46,9 +46,11 @@ def build_parser():
     ap.add_argument("--n-global", type=C.parse_size, default=28672, help="global N, sharded (used when --n is 0)")
     ap.add_argument("--gather-rows", default="128,512,2048,4096")
     ap.add_argument("--modes", default="fused,ce,nccl")
+    ap.add_argument("--transport", default="push", choices=["push", "pull"], help="fused mode: gather warps store the own shard to every peer (push) or load the peers' shards (pull)")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--cta-group", type=int, default=2)
+    ap.add_argument("--ablate", type=int, default=0, help="timing-only knob of the fused mode: 4 = the TMA producer does not wait for gathered rows")
     ap.add_argument("--verify", action="store_true")
     ap.add_argument("--csv", default=None)
     return ap
@@ -141,13 +143,13 @@ def main(argv=None) -> int:
         S = seg // g
         for mode in [m for m in modes if m in ("fused", "ce")]:
             if mode == "fused":
-                op = AgGemm(heap, M, K, Bt, cta_group=args.cta_group, gather_rows=g, out=out)
+                op = AgGemm(heap, M, K, Bt, cta_group=args.cta_group, gather_rows=g, out=out, ablate=args.ablate, transport=args.transport)
                 ctrl = None
                 a_full = op.a_full
                 op.a_shard.copy_(shard)
                 run_ovl = lambda: op()
                 # t_seg: same kernel, same tile order, no waiting (data already gathered)
-                seg_op = AgGemm(heap, M, K, Bt, cta_group=args.cta_group, gather_rows=g, out=out, comm_enabled=False)
+                seg_op = AgGemm(heap, M, K, Bt, cta_group=args.cta_group, gather_rows=g, out=out, comm_enabled=False, transport=args.transport)
                 seg_op.a_full.copy_(gathered)
                 run_seg = lambda: seg_op()
                 run_comm = None

@@ -81,7 +81,8 @@ struct GemmParams {
   int world, rank;
   int epoch;      // 1-based call number of the plan that owns the flag buffers
   int comm_enabled;
-  int ablate;     // experiment knobs: bit 0 = no reduce warps, bit 1 = no tile signals (timing only)
+  int ablate;     // experiment knobs (timing only): bit 0 = no reduce warps, bit 1 = no tile signals,
+                  // bit 2 = AG+GEMM producer does not wait for gathered rows
 
   // Output routing.  Rows are split in segments of seg_rows; row r of segment
   // s goes to dst_base[s] + (dst_row_off[s] + r - s * seg_rows) * ldc.
@@ -105,6 +106,10 @@ struct GemmParams {
   int gather_rows;
   int* ag_done;                            // local: gather warps that finished (monotonic)
   int* ag_read_done[kMaxWorld];            // rank s's "peers done reading me" counter
+  // Push form of the all-gather: every rank stores its own shard into every peer's gathered buffer.
+  int ag_push;                             // 0 = pull (loads from peers), 1 = push (stores to peers)
+  __nv_bfloat16* ag_dst[kMaxWorld];        // rank s's gathered buffer [M][K] (a peer pointer)
+  int* ag_flag_peer[kMaxWorld];            // rank s's row-block counters
 
   // Start barrier: rank s's arrival counter.
   int* barrier[kMaxWorld];
@@ -303,12 +308,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         sched.tile(t, &m_blk, &n_blk);
         const int m0 = m_blk * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BM;
         const int n0 = n_blk * Cfg::BN + static_cast<int>(cta_rank) * Cfg::B_ROWS;
-        if (p.mode == kModeAgGemm && fused_comm && (m0 / p.seg_rows) != p.rank) {
+        if (p.mode == kModeAgGemm && fused_comm && !(p.ablate & 4) && (m0 / p.seg_rows) != p.rank) {
           // Rows [m0, m0+BM) lie in one gather block (gather_rows % BM == 0).
           const int blk = m0 / p.gather_rows;
           const int target = p.epoch * (p.gather_rows / Cfg::GATHER_ITEM_ROWS);
           int seen = 0;
-          if (!wait_ge<false>(p.ag_flags + blk, target, s_abort, deadline, &seen)) {
+          const bool landed = p.ag_push ? wait_ge<true>(p.ag_flags + blk, target, s_abort, deadline, &seen)
+                                        : wait_ge<false>(p.ag_flags + blk, target, s_abort, deadline, &seen);
+          if (!landed) {
             detail::report(p, s_abort, kErrAgFlag, blk, seen);
             ok = false;
             break;
@@ -558,7 +565,41 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
       good = __shfl_sync(0xffffffffu, good, 0);
-      if (good) {
+      if (good && p.ag_push) {
+        // ---- push: store this rank's own shard into every peer's gathered buffer.  Stores need no
+        // round trip, so a few warps per SM reach the link rate; items go out in row order, which is
+        // the order in which every consumer's schedule needs them. ----
+        const int items = p.seg_rows / Cfg::GATHER_ITEM_ROWS;
+        const int gw = blockIdx.x * Cfg::COMM_WARPS + cw;
+        const int n_gw = gridDim.x * Cfg::COMM_WARPS;
+        const size_t item_bytes = static_cast<size_t>(Cfg::GATHER_ITEM_ROWS) * p.K * 2;
+        for (int j = gw; j < items; j += n_gw) {
+          const size_t grow = static_cast<size_t>(p.rank) * p.seg_rows + static_cast<size_t>(j) * Cfg::GATHER_ITEM_ROWS;
+          const size_t boff = grow * p.K * 2;
+          const char* src = reinterpret_cast<const char*>(p.ag_full) + boff;
+          constexpr int kUnroll = 4;
+          size_t off = static_cast<size_t>(lane) * 16;
+          for (; off + (kUnroll - 1) * 512 < item_bytes; off += kUnroll * 512) {
+            uint4 w[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) w[u] = ld_v4_stream(src + off + u * 512);
+            for (int step = 1; step < p.world; ++step) {
+              char* dst = reinterpret_cast<char*>(p.ag_dst[(p.rank + step) % p.world]) + boff;
+#pragma unroll
+              for (int u = 0; u < kUnroll; ++u) st_v4(dst + off + u * 512, w[u]);
+            }
+          }
+          for (; off < item_bytes; off += 512) {
+            const uint4 w = ld_v4_stream(src + off);
+            for (int step = 1; step < p.world; ++step)
+              st_v4(reinterpret_cast<char*>(p.ag_dst[(p.rank + step) % p.world]) + boff + off, w);
+          }
+          // Every lane's stores are performed at system scope, then one lane per peer signals.
+          fence_sys();
+          __syncwarp();
+          if (lane < p.world && lane != p.rank) red_relaxed_sys_add(p.ag_flag_peer[lane] + static_cast<int>(grow / p.gather_rows), 1);
+        }
+      } else if (good) {
         const int items_per_seg = p.seg_rows / Cfg::GATHER_ITEM_ROWS;
         const int total = (p.world - 1) * items_per_seg;
         const int gw = blockIdx.x * Cfg::COMM_WARPS + cw;

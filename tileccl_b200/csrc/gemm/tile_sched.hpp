@@ -27,7 +27,9 @@ namespace tcl {
 enum MOrder : int {
   kOrderPlain = 0,   // schedule row p is tile row p
   kOrderRsPush = 1,  // reduce-scatter: rounds of chunks, peers rotated, own segment last
-  kOrderAgPull = 2   // all-gather: own segment first, then peers in rotation
+  kOrderAgPull = 2,  // all-gather by pull: own segment first, then peers in rotation, one after the other
+  kOrderAgPush = 3   // all-gather by push: own segment first, then tile row i of every peer before row i+1
+                     // (all shards arrive at the same rate, so rows are consumed in arrival order)
 };
 
 struct TileSched {
@@ -54,6 +56,14 @@ struct TileSched {
       const int i = q - step * cpr;
       const int seg = (rank + 1 + step) % world;  // own segment at the last step
       return seg * st + g * cpr + i;
+    }
+    if (order == kOrderAgPush) {
+      const int st = seg_tiles();
+      if (p < st) return rank * st + p;             // own segment
+      const int q = p - st;
+      const int i = q / (world - 1);                // tile row inside the segments
+      const int step = q - i * (world - 1) + 1;     // 1 .. world-1
+      return ((rank + step) % world) * st + i;
     }
     if (order == kOrderAgPull) {
       const int st = seg_tiles();

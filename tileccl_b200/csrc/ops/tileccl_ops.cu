@@ -236,6 +236,8 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
     p.rs_tile_cnt[s] = d->rs_tile_cnt[s];
     p.ag_src[s] = static_cast<const __nv_bfloat16*>(d->ag_src[s]);
     p.ag_read_done[s] = d->ag_read_done[s];
+    p.ag_dst[s] = static_cast<__nv_bfloat16*>(d->ag_dst[s]);
+    p.ag_flag_peer[s] = d->ag_flag_peer[s];
     p.barrier[s] = d->barrier[s];
   }
   p.status = d->status;
@@ -279,7 +281,13 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
   } else if (d->mode == TCL_MODE_AG_GEMM) {
     if (nseg != d->world) return fail("AG+GEMM: M / seg_rows must equal world");
     if (d->lda != d->K) return fail("AG+GEMM: gathered A must be dense (lda == K)");
-    sc.order = kOrderAgPull; sc.world = d->world; sc.rank = d->rank;
+    sc.order = d->ag_push ? kOrderAgPush : kOrderAgPull; sc.world = d->world; sc.rank = d->rank;
+    p.ag_push = d->ag_push;
+    if (d->ag_push && d->group_m <= 0 && d->world > 1) {
+      // keep one raster group inside a band of schedule rows that arrive together
+      const int band = d->world - 1;
+      sc.group_m = band >= 4 ? band : band * (8 / band > 0 ? 8 / band : 1);
+    }
     if (d->comm_enabled && d->world > 1) {
       if (d->gather_rows < 128 || d->gather_rows % tile_m != 0 && d->gather_rows % 128 != 0)
         return fail("AG+GEMM: gather_rows must be a multiple of 128");
@@ -289,6 +297,7 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
       for (int s = 0; s < d->world; ++s) {
         if (!d->ag_src[s] || !d->ag_read_done[s] || !d->barrier[s])
           return fail("AG+GEMM: peer pointers missing for a rank");
+        if (d->ag_push && (!d->ag_dst[s] || !d->ag_flag_peer[s])) return fail("AG+GEMM push: peer buffers missing for a rank");
         if (reinterpret_cast<uintptr_t>(d->ag_src[s]) & 15) return fail("AG+GEMM: ag_src must be 16-byte aligned");
       }
     }

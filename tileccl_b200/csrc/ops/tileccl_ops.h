@@ -45,6 +45,9 @@ typedef struct tcl_gemm_desc {
   int32_t gather_rows;
   int32_t* ag_done;
   int32_t* ag_read_done[TCL_MAX_WORLD];
+  int32_t ag_push;       /* 0 = gather warps load from peers, 1 = they store the own shard to every peer */
+  void* ag_dst[TCL_MAX_WORLD];        /* push: rank s's gathered buffer */
+  int32_t* ag_flag_peer[TCL_MAX_WORLD]; /* push: rank s's row-block counters */
   /* common */
   int32_t* barrier[TCL_MAX_WORLD];
   int32_t* status;      /* 4 ints, zeroed by the caller */

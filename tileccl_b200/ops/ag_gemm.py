@@ -23,10 +23,13 @@ from ._plan import Plan, require_bf16_rowmajor
 class AgGemm:
     def __init__(self, heap: SymmetricHeap, M: int, K: int, Bt: torch.Tensor, cta_group: int = 2,
                  gather_rows: int = 512, out: torch.Tensor | None = None, group_m: int = 0,
-                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0):
+                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "push"):
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
         world, rank = heap.world, heap.rank
+        if transport not in ("push", "pull"):
+            raise ValueError("transport must be 'push' or 'pull'")
+        self.transport = transport
         N = Bt.shape[0]
         if Bt.shape[1] != K:
             raise ValueError("Bt must be [N, K]")
@@ -59,11 +62,15 @@ class AgGemm:
             d.ag_src[s] = heap.peer_ptr(self.a_full, s) + s * seg * K * 2
             d.ag_read_done[s] = heap.peer_ptr(self.done, s) + 16 * 4
             d.barrier[s] = heap.peer_ptr(self.barrier, s)
+            d.ag_dst[s] = heap.peer_ptr(self.a_full, s)
+            d.ag_flag_peer[s] = heap.peer_ptr(self.flags, s)
+        d.ag_push = 1 if transport == "push" else 0
         d.ag_flags = self.flags.data_ptr()
         d.gather_rows = gather_rows
         d.ag_done = self.done.data_ptr()
         d.timeout_ns = int(timeout_ms * 1e6)
         d.group_m, d.num_ctas = group_m, num_ctas
+        d.ablate = ablate
         self.plan = Plan(d, keep_alive=(Bt, out, self.a_full, self.flags, self.done, self.barrier))
         self.gather_rows = gather_rows
 
@@ -79,7 +86,7 @@ class AgGemm:
         epoch * (gather_rows / 8) arrivals, the local segment's flags were never touched, and all
         peers reported that they finished reading this rank's shard.  Synchronises."""
         h = self.heap
-        if h.world == 1 or not self.plan.desc.comm_enabled:
+        if h.world == 1 or not self.plan.desc.comm_enabled or self.plan.desc.ablate:
             return
         M = self.a_full.shape[0]
         seg = M // h.world
@@ -89,7 +96,7 @@ class AgGemm:
             own = (b * self.gather_rows) // seg == h.rank
             if v != (0 if own else per):
                 raise AssertionError(f"gather flag {b} is {v}, expected {0 if own else per}")
-        if int(self.done[16]) != self.plan.epoch * (h.world - 1):
+        if self.transport == "pull" and int(self.done[16]) != self.plan.epoch * (h.world - 1):
             raise AssertionError("not every peer reported the end of its reads")
 
     @property

@@ -8,7 +8,7 @@ the XOR segment swizzle of its fused kernel
 """
 from __future__ import annotations
 
-ORDER_PLAIN, ORDER_RS_PUSH, ORDER_AG_PULL = 0, 1, 2
+ORDER_PLAIN, ORDER_RS_PUSH, ORDER_AG_PULL, ORDER_AG_PUSH = 0, 1, 2, 3
 TILE_N = 256
 CTA_M = 128
 
@@ -23,6 +23,11 @@ def m_of_row(p: int, m_tiles: int, order: int = ORDER_PLAIN, world: int = 1, ran
         step, i = divmod(q, cpr)
         seg = (rank + 1 + step) % world
         return seg * st + g * cpr + i
+    if order == ORDER_AG_PUSH:
+        if p < st:
+            return rank * st + p
+        i, step = divmod(p - st, world - 1)
+        return ((rank + step + 1) % world) * st + i
     if order == ORDER_AG_PULL:
         step, i = divmod(p, st)
         return ((rank + step) % world) * st + i
