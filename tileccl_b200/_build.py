@@ -30,6 +30,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--thre
 
 # Shared library: sources relative to csrc/.
 LIB_NAME = "libtileccl.so"
+DEBUG_LIB_NAME = "libtileccl_debug.so"
 LIB_SOURCES = [
     "ops/tileccl_ops.cu",
     "runtime/symm_heap.cu",
@@ -81,8 +82,8 @@ def _run(cmd: list[str], verbose: bool) -> None:
         print(r.stderr, flush=True)
 
 
-def _compile(src: Path, verbose: bool, extra: list[str]) -> Path:
-    obj = OBJ_DIR / (str(src.relative_to(CSRC)).replace("/", "_") + ".o")
+def _compile(src: Path, verbose: bool, extra: list[str], tag: str = "") -> Path:
+    obj = OBJ_DIR / (str(src.relative_to(CSRC)).replace("/", "_") + tag + ".o")
     if _stale(obj, [src]):
         _run([nvcc(), *ARCH_FLAGS, *COMMON_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)], verbose)
     return obj
@@ -106,6 +107,12 @@ def build(verbose: bool = False, programs: bool = True, ptxas_info: bool = False
         if _stale(lib_out, objs) or any(o.stat().st_mtime > lib_out.stat().st_mtime for o in objs):
             _run([nvcc(), *ARCH_FLAGS, "-shared", "-o", str(lib_out), *map(str, objs)], verbose)
         outputs[LIB_NAME] = lib_out
+        # Debug variant: the same sources with device-side address checks (TCL_DEBUG_BOUNDS).
+        dbg_out = LIB_DIR / DEBUG_LIB_NAME
+        dobjs = list(ex.map(lambda s: _compile(s, verbose, extra + ["-DTCL_DEBUG_BOUNDS"], ".dbg"), lib_srcs))
+        if _stale(dbg_out, dobjs) or any(o.stat().st_mtime > dbg_out.stat().st_mtime for o in dobjs):
+            _run([nvcc(), *ARCH_FLAGS, "-shared", "-o", str(dbg_out), *map(str, dobjs)], verbose)
+        outputs[DEBUG_LIB_NAME] = dbg_out
 
         if programs:
             def one(item):

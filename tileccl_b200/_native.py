@@ -13,7 +13,10 @@ MAX_WORLD = 8
 MODE_PLAIN, MODE_GEMM_RS, MODE_AG_GEMM = 0, 1, 2
 ORDER_PLAIN, ORDER_RS_PUSH, ORDER_AG_PULL, ORDER_AG_PUSH = 0, 1, 2, 3
 
-_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtileccl.so"
+import os as _os
+
+# TILECCL_DEBUG=1 selects the build with device-side address checks (libtileccl_debug.so).
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / ("libtileccl_debug.so" if _os.environ.get("TILECCL_DEBUG") == "1" else "libtileccl.so")
 
 
 class GemmDesc(C.Structure):
@@ -55,6 +58,8 @@ class GemmDesc(C.Structure):
         ("group_m", C.c_int32),
         ("num_ctas", C.c_int32),
         ("rs_mc_stage", C.c_void_p),
+        ("range_lo", C.c_uint64 * MAX_WORLD),
+        ("range_hi", C.c_uint64 * MAX_WORLD),
         ("ablate", C.c_int32),
     ]
 
@@ -96,6 +101,7 @@ def lib() -> C.CDLL:
     sig("tcl_fill_normal_bf16", i32, [vp, i64, u64, C.c_float, C.c_float, vp])
     sig("tcl_max_rel_err", i32, [vp, vp, i64, vp, vp, vp])
     sig("tcl_status_string", C.c_char_p, [i32])
+    sig("tcl_debug_bounds_enabled", i32, [])
     # symmetric heap
     sig("tcl_heap_alloc", i32, [C.c_size_t, C.POINTER(vp)])
     sig("tcl_heap_free", i32, [vp])

@@ -70,7 +70,8 @@ enum GemmStatus : int {
   kErrStartBarrier = 5,    // a peer never arrived at the start barrier
   kErrRsTileCount = 6,     // reduce warps: a tile never got all its partials
   kErrAgFlag = 7,          // TMA producer: a gathered row block never arrived
-  kErrAgEndBarrier = 8     // a peer never finished reading this rank's shard
+  kErrAgEndBarrier = 8,    // a peer never finished reading this rank's shard
+  kErrBounds = 9           // debug build only: an address fell outside the range it must stay in (access skipped)
 };
 
 struct GemmParams {
@@ -114,6 +115,11 @@ struct GemmParams {
   // Start barrier: rank s's arrival counter.
   int* barrier[kMaxWorld];
 
+  // Debug build (TCL_DEBUG_BOUNDS): every data address that may be remote is checked against the
+  // mapping of the rank it targets before it is used; a bad one is recorded and the access skipped.
+  unsigned long long range_lo[kMaxWorld];
+  unsigned long long range_hi[kMaxWorld];
+
   int* status;                   // [4]: code, blockIdx, detail0, detail1
   unsigned long long timeout_ns;
 };
@@ -153,6 +159,18 @@ __device__ __forceinline__ void report(const GemmParams& p, volatile int* s_abor
     p.status[3] = d1;
   }
   *s_abort = 1;
+}
+
+// Debug-build address check: true if [addr, addr + bytes) lies inside rank `r`'s mapped range.
+__device__ __forceinline__ bool in_range(const GemmParams& p, volatile int* s_abort, int r, const void* addr, unsigned bytes) {
+#ifdef TCL_DEBUG_BOUNDS
+  const unsigned long long a = reinterpret_cast<unsigned long long>(addr);
+  if (a < p.range_lo[r] || a + bytes > p.range_hi[r]) {
+    report(p, s_abort, kErrBounds, r, static_cast<int>((a - p.range_lo[r]) >> 4));
+    return false;
+  }
+#endif
+  return true;
 }
 
 // Sums the `kWorld` staged bf16 partials of one 128x256 tile in fp32 and writes
@@ -498,7 +516,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint4 w = lds_v4(my_buf + r * 256 + ((ch ^ (r & 7)) << 4));
           const int grow = row0 + q * 32 + r;
           if (grow < p.M && col0 + ccol < p.N) {
-            st_v4(dst0 + static_cast<long long>(q * 32 + r) * p.ldc + ccol, w);
+            __nv_bfloat16* a = dst0 + static_cast<long long>(q * 32 + r) * p.ldc + ccol;
+            // in GEMM+RS the row segment is the destination rank
+            if (p.mode != kModeGemmRs || detail::in_range(p, s_abort, seg, a, 16)) st_v4(a, w);
           }
         }
         __syncwarp();   // the buffer is rewritten by the next pair of reads
@@ -584,7 +604,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) w[u] = ld_v4_stream(src + off + u * 512);
             for (int step = 1; step < p.world; ++step) {
-              char* dst = reinterpret_cast<char*>(p.ag_dst[(p.rank + step) % p.world]) + boff;
+              const int peer = (p.rank + step) % p.world;
+              char* dst = reinterpret_cast<char*>(p.ag_dst[peer]) + boff;
+              if (!detail::in_range(p, s_abort, peer, dst + off, kUnroll * 512)) continue;
 #pragma unroll
               for (int u = 0; u < kUnroll; ++u) st_v4(dst + off + u * 512, w[u]);
             }
@@ -611,6 +633,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int seg = (p.rank + step) % p.world;
           const size_t row_in_seg = static_cast<size_t>(i) * Cfg::GATHER_ITEM_ROWS;
           const char* src = reinterpret_cast<const char*>(p.ag_src[seg] + row_in_seg * p.K);
+          if (!detail::in_range(p, s_abort, seg, src, static_cast<unsigned>(item_bytes))) continue;
           const size_t grow = static_cast<size_t>(seg) * p.seg_rows + row_in_seg;
           char* dst = reinterpret_cast<char*>(p.ag_full + grow * p.K);
           // Two register banks of 8 x 16 bytes per lane: the loads of one 4 KiB step are issued

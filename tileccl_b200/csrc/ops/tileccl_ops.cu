@@ -237,6 +237,8 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
     p.ag_src[s] = static_cast<const __nv_bfloat16*>(d->ag_src[s]);
     p.ag_read_done[s] = d->ag_read_done[s];
     p.ag_dst[s] = static_cast<__nv_bfloat16*>(d->ag_dst[s]);
+    p.range_lo[s] = d->range_lo[s];
+    p.range_hi[s] = d->range_hi[s] ? d->range_hi[s] : ~0ull;
     p.ag_flag_peer[s] = d->ag_flag_peer[s];
     p.barrier[s] = d->barrier[s];
   }
@@ -389,6 +391,14 @@ int tcl_max_rel_err(const void* got_bf16, const float* ref, int64_t n, float* sc
   return static_cast<int>(cudaGetLastError());
 }
 
+int tcl_debug_bounds_enabled(void) {
+#ifdef TCL_DEBUG_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 const char* tcl_status_string(int code) {
   switch (code) {
     case kOk: return "ok";
@@ -400,6 +410,7 @@ const char* tcl_status_string(int code) {
     case kErrRsTileCount: return "reduce warps timed out waiting for a tile's partials";
     case kErrAgFlag: return "TMA producer timed out waiting for a gathered row block";
     case kErrAgEndBarrier: return "a peer never finished reading this rank's shard";
+    case kErrBounds: return "debug build: an address fell outside its rank's mapped range (access skipped)";
     default: return "unknown status";
   }
 }

@@ -55,6 +55,8 @@ typedef struct tcl_gemm_desc {
   int32_t group_m;      /* raster group height; 0 = default */
   int32_t num_ctas;     /* 0 = one per SM */
   const void* rs_mc_stage; /* GEMM+RS NVLS variant: multicast mapping of the [M][N] staging buffer, else NULL */
+  uint64_t range_lo[TCL_MAX_WORLD]; /* debug build: mapped range of the memory of rank s that this plan may touch */
+  uint64_t range_hi[TCL_MAX_WORLD];
   int32_t ablate;       /* experiments only: bit 0 = no reduce warps, bit 1 = no tile signals */
 } tcl_gemm_desc;
 
@@ -89,6 +91,8 @@ int tcl_max_rel_err(const void* got_bf16, const float* ref, int64_t n, float* sc
                     float* result, void* stream);
 
 const char* tcl_status_string(int code);
+/* 1 if the library was built with TCL_DEBUG_BOUNDS (address checks on every possibly-remote access). */
+int tcl_debug_bounds_enabled(void);
 
 #ifdef __cplusplus
 }

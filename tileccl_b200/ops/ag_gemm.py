@@ -66,6 +66,9 @@ class AgGemm:
             d.ag_flag_peer[s] = heap.peer_ptr(self.flags, s)
         d.ag_push = 1 if transport == "push" else 0
         d.ag_flags = self.flags.data_ptr()
+        for s in range(world):   # debug build: the only memory of rank s this plan may touch is its heap
+            d.range_lo[s] = heap.base[s]
+            d.range_hi[s] = heap.base[s] + heap.nbytes
         d.gather_rows = gather_rows
         d.ag_done = self.done.data_ptr()
         d.timeout_ns = int(timeout_ms * 1e6)

@@ -84,6 +84,9 @@ class GemmRs:
             d.rs_tile_cnt[s] = heap.peer_ptr(self.tile_cnt, s)
             d.barrier[s] = heap.peer_ptr(self.barrier, s)
         d.rs_stage = self.stage.data_ptr()
+        for s in range(world):   # debug build: the only memory of rank s this plan may touch is its heap
+            d.range_lo[s] = heap.base[s]
+            d.range_hi[s] = heap.base[s] + heap.nbytes
         d.rs_out = self.out.data_ptr()
         d.ld_out = N
         d.rs_chunks = rs_chunks
