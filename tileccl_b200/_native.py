@@ -102,6 +102,9 @@ def lib() -> C.CDLL:
     sig("tcl_max_rel_err", i32, [vp, vp, i64, vp, vp, vp])
     sig("tcl_status_string", C.c_char_p, [i32])
     sig("tcl_debug_bounds_enabled", i32, [])
+    sig("tcl_make_smem_desc_k_sw128", u64, [C.c_uint32])
+    sig("tcl_advance_desc_k", u64, [u64, C.c_uint32])
+    sig("tcl_make_idesc_bf16_f32", C.c_uint32, [C.c_uint32, C.c_uint32])
     # symmetric heap
     sig("tcl_heap_alloc", i32, [C.c_size_t, C.POINTER(vp)])
     sig("tcl_heap_free", i32, [vp])

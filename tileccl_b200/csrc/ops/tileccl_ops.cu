@@ -83,14 +83,11 @@ __global__ void barrier_all_kernel(BarrierArgs a, int world, int rank, int epoch
 // ---------------------------------------------------------------------------
 __global__ void silu_mul_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, long long rows,
                                 long long ffn8) {
-  // One thread per 8 output elements; a row of gu holds 2*ffn8 chunks.
+  // One thread per 8 output elements; a row of gu holds 2*ffn8 chunks.  Two independent chunks
+  // (four 16-byte loads) are in flight per thread per iteration.
   const long long total = rows * ffn8;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / ffn8;
-    const long long c = i - r * ffn8;
-    const uint4 g = gu[r * 2 * ffn8 + c];
-    const uint4 u = gu[r * 2 * ffn8 + ffn8 + c];
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  auto one = [](const uint4& g, const uint4& u) {
     const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
     const uint32_t uw[4] = {u.x, u.y, u.z, u.w};
     uint32_t ow[4];
@@ -102,7 +99,20 @@ __global__ void silu_mul_kernel(const uint4* __restrict__ gu, uint4* __restrict_
       const float o1 = g1 / (1.f + __expf(-g1)) * u1;
       ow[e] = ptx::pack_bf16x2(__float_as_uint(o0), __float_as_uint(o1));
     }
-    out[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    return make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  };
+  long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  for (; i + stride < total; i += 2 * stride) {
+    const long long j = i + stride;
+    const long long r0 = i / ffn8, c0 = i - r0 * ffn8, r1 = j / ffn8, c1 = j - r1 * ffn8;
+    const uint4 ga = gu[r0 * 2 * ffn8 + c0], ua = gu[r0 * 2 * ffn8 + ffn8 + c0];
+    const uint4 gb = gu[r1 * 2 * ffn8 + c1], ub = gu[r1 * 2 * ffn8 + ffn8 + c1];
+    out[i] = one(ga, ua);
+    out[j] = one(gb, ub);
+  }
+  for (; i < total; i += stride) {
+    const long long r = i / ffn8, c = i - r * ffn8;
+    out[i] = one(gu[r * 2 * ffn8 + c], gu[r * 2 * ffn8 + ffn8 + c]);
   }
 }
 
@@ -390,6 +400,11 @@ int tcl_max_rel_err(const void* got_bf16, const float* ref, int64_t n, float* sc
   max_rel_err_final<<<1, 256, 0, st>>>(scratch, static_cast<int>(blocks), result);
   return static_cast<int>(cudaGetLastError());
 }
+
+// Descriptor encoders, exposed so that their bit layouts can be checked on a machine without a GPU.
+uint64_t tcl_make_smem_desc_k_sw128(uint32_t smem_addr) { return tcl::ptx::make_smem_desc_k_sw128(smem_addr); }
+uint64_t tcl_advance_desc_k(uint64_t desc, uint32_t bytes) { return tcl::ptx::advance_desc_k(desc, bytes); }
+uint32_t tcl_make_idesc_bf16_f32(uint32_t m, uint32_t n) { return tcl::ptx::make_idesc_bf16_f32(m, n); }
 
 int tcl_debug_bounds_enabled(void) {
 #ifdef TCL_DEBUG_BOUNDS

@@ -90,6 +90,11 @@ int tcl_fill_normal_bf16(void* dst, int64_t n, uint64_t seed, float mean, float 
 int tcl_max_rel_err(const void* got_bf16, const float* ref, int64_t n, float* scratch,
                     float* result, void* stream);
 
+/* tcgen05 descriptor encoders (host-callable, for layout tests). */
+uint64_t tcl_make_smem_desc_k_sw128(uint32_t smem_addr);
+uint64_t tcl_advance_desc_k(uint64_t desc, uint32_t bytes);
+uint32_t tcl_make_idesc_bf16_f32(uint32_t m, uint32_t n);
+
 const char* tcl_status_string(int code);
 /* 1 if the library was built with TCL_DEBUG_BOUNDS (address checks on every possibly-remote access). */
 int tcl_debug_bounds_enabled(void);
