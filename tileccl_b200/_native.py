@@ -47,6 +47,7 @@ class GemmDesc(C.Structure):
         ("ag_src", C.c_void_p * MAX_WORLD),
         ("ag_flags", C.c_void_p),
         ("gather_rows", C.c_int32),
+        ("ag_item_rows", C.c_int32),
         ("ag_done", C.c_void_p),
         ("ag_read_done", C.c_void_p * MAX_WORLD),
         ("ag_push", C.c_int32),

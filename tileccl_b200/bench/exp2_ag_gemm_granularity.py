@@ -51,6 +51,7 @@ def build_parser():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--cta-group", type=int, default=2)
     ap.add_argument("--ablate", type=int, default=0, help="timing-only knob of the fused mode: 4 = the TMA producer does not wait for gathered rows")
+    ap.add_argument("--item-rows", type=int, default=1, help="rows per gather work item of the fused mode")
     ap.add_argument("--verify", action="store_true")
     ap.add_argument("--csv", default=None)
     return ap
@@ -143,7 +144,7 @@ def main(argv=None) -> int:
         S = seg // g
         for mode in [m for m in modes if m in ("fused", "ce")]:
             if mode == "fused":
-                op = AgGemm(heap, M, K, Bt, cta_group=args.cta_group, gather_rows=g, out=out, ablate=args.ablate, transport=args.transport)
+                op = AgGemm(heap, M, K, Bt, cta_group=args.cta_group, gather_rows=g, out=out, ablate=args.ablate, transport=args.transport, item_rows=args.item_rows)
                 ctrl = None
                 a_full = op.a_full
                 op.a_shard.copy_(shard)

@@ -105,6 +105,8 @@ struct GemmParams {
   __nv_bfloat16* ag_full;                  // local gathered A [M][K]
   int* ag_flags;                           // local counters, one per gather_rows row block
   int gather_rows;
+  int ag_item_rows;                        // rows one gather warp moves per work item (and per counter arrival);
+                                           // small items make rows land progressively, in schedule order
   int* ag_done;                            // local: gather warps that finished (monotonic)
   int* ag_read_done[kMaxWorld];            // rank s's "peers done reading me" counter
   // Push form of the all-gather: every rank stores its own shard into every peer's gathered buffer.
@@ -146,7 +148,6 @@ struct GemmCfg {
   static constexpr int TMEM_COLS = 512;             // two accumulator buffers of BN columns
   static constexpr int CTRL_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES + 1024;
-  static constexpr int GATHER_ITEM_ROWS = 8;
 };
 
 namespace detail {
@@ -329,7 +330,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (p.mode == kModeAgGemm && fused_comm && !(p.ablate & 4) && (m0 / p.seg_rows) != p.rank) {
           // Rows [m0, m0+BM) lie in one gather block (gather_rows % BM == 0).
           const int blk = m0 / p.gather_rows;
-          const int target = p.epoch * (p.gather_rows / Cfg::GATHER_ITEM_ROWS);
+          const int target = p.epoch * (p.gather_rows / p.ag_item_rows);
           int seen = 0;
           const bool landed = p.ag_push ? wait_ge<true>(p.ag_flags + blk, target, s_abort, deadline, &seen)
                                         : wait_ge<false>(p.ag_flags + blk, target, s_abort, deadline, &seen);
@@ -589,12 +590,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // ---- push: store this rank's own shard into every peer's gathered buffer.  Stores need no
         // round trip, so a few warps per SM reach the link rate; items go out in row order, which is
         // the order in which every consumer's schedule needs them. ----
-        const int items = p.seg_rows / Cfg::GATHER_ITEM_ROWS;
+        const int items = p.seg_rows / p.ag_item_rows;
         const int gw = blockIdx.x * Cfg::COMM_WARPS + cw;
         const int n_gw = gridDim.x * Cfg::COMM_WARPS;
-        const size_t item_bytes = static_cast<size_t>(Cfg::GATHER_ITEM_ROWS) * p.K * 2;
+        const size_t item_bytes = static_cast<size_t>(p.ag_item_rows) * p.K * 2;
         for (int j = gw; j < items; j += n_gw) {
-          const size_t grow = static_cast<size_t>(p.rank) * p.seg_rows + static_cast<size_t>(j) * Cfg::GATHER_ITEM_ROWS;
+          const size_t grow = static_cast<size_t>(p.rank) * p.seg_rows + static_cast<size_t>(j) * p.ag_item_rows;
           const size_t boff = grow * p.K * 2;
           const char* src = reinterpret_cast<const char*>(p.ag_full) + boff;
           constexpr int kUnroll = 4;
@@ -622,16 +623,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (lane < p.world && lane != p.rank) red_relaxed_sys_add(p.ag_flag_peer[lane] + static_cast<int>(grow / p.gather_rows), 1);
         }
       } else if (good) {
-        const int items_per_seg = p.seg_rows / Cfg::GATHER_ITEM_ROWS;
+        const int items_per_seg = p.seg_rows / p.ag_item_rows;
         const int total = (p.world - 1) * items_per_seg;
         const int gw = blockIdx.x * Cfg::COMM_WARPS + cw;
         const int n_gw = gridDim.x * Cfg::COMM_WARPS;
-        const size_t item_bytes = static_cast<size_t>(Cfg::GATHER_ITEM_ROWS) * p.K * 2;
+        const size_t item_bytes = static_cast<size_t>(p.ag_item_rows) * p.K * 2;
         for (int j = gw; j < total; j += n_gw) {
           const int step = j / items_per_seg + 1;
           const int i = j - (step - 1) * items_per_seg;
           const int seg = (p.rank + step) % p.world;
-          const size_t row_in_seg = static_cast<size_t>(i) * Cfg::GATHER_ITEM_ROWS;
+          const size_t row_in_seg = static_cast<size_t>(i) * p.ag_item_rows;
           const char* src = reinterpret_cast<const char*>(p.ag_src[seg] + row_in_seg * p.K);
           if (!detail::in_range(p, s_abort, seg, src, static_cast<unsigned>(item_bytes))) continue;
           const size_t grow = static_cast<size_t>(seg) * p.seg_rows + row_in_seg;

@@ -317,6 +317,8 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
     p.ag_flags = d->ag_flags;
     p.gather_rows = d->gather_rows > 0 ? d->gather_rows : d->seg_rows;
     p.ag_done = d->ag_done;
+    p.ag_item_rows = d->ag_item_rows > 0 ? d->ag_item_rows : 1;
+    if (p.gather_rows % p.ag_item_rows != 0) return fail("AG+GEMM: ag_item_rows must divide gather_rows");
   } else if (d->mode != TCL_MODE_PLAIN) {
     return fail("unknown mode");
   } else {

@@ -43,6 +43,7 @@ typedef struct tcl_gemm_desc {
   const void* ag_src[TCL_MAX_WORLD];
   int32_t* ag_flags;
   int32_t gather_rows;
+  int32_t ag_item_rows; /* rows per gather work item; 0 = 1 row */
   int32_t* ag_done;
   int32_t* ag_read_done[TCL_MAX_WORLD];
   int32_t ag_push;       /* 0 = gather warps load from peers, 1 = they store the own shard to every peer */

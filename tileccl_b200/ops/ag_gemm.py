@@ -23,7 +23,7 @@ from ._plan import Plan, require_bf16_rowmajor
 class AgGemm:
     def __init__(self, heap: SymmetricHeap, M: int, K: int, Bt: torch.Tensor, cta_group: int = 2,
                  gather_rows: int = 512, out: torch.Tensor | None = None, group_m: int = 0,
-                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "push"):
+                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "push", item_rows: int = 1):
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
         world, rank = heap.world, heap.rank
@@ -70,6 +70,8 @@ class AgGemm:
             d.range_lo[s] = heap.base[s]
             d.range_hi[s] = heap.base[s] + heap.nbytes
         d.gather_rows = gather_rows
+        d.ag_item_rows = item_rows
+        self.item_rows = item_rows
         d.ag_done = self.done.data_ptr()
         d.timeout_ns = int(timeout_ms * 1e6)
         d.group_m, d.num_ctas = group_m, num_ctas
@@ -86,14 +88,14 @@ class AgGemm:
 
     def audit(self) -> None:
         """Flag audit after a run: every gathered row block of a peer segment stands at
-        epoch * (gather_rows / 8) arrivals, the local segment's flags were never touched, and all
+        epoch * (gather_rows / item_rows) arrivals, the local segment's flags were never touched, and all
         peers reported that they finished reading this rank's shard.  Synchronises."""
         h = self.heap
         if h.world == 1 or not self.plan.desc.comm_enabled or self.plan.desc.ablate:
             return
         M = self.a_full.shape[0]
         seg = M // h.world
-        per = self.gather_rows // 8 * self.plan.epoch
+        per = self.gather_rows // self.item_rows * self.plan.epoch
         flags = self.flags[: M // self.gather_rows].tolist()
         for b, v in enumerate(flags):
             own = (b * self.gather_rows) // seg == h.rank
