@@ -46,7 +46,7 @@ def build_parser():
     ap.add_argument("--n-global", type=C.parse_size, default=28672, help="global N, sharded (used when --n is 0)")
     ap.add_argument("--gather-rows", default="128,512,2048,4096")
     ap.add_argument("--modes", default="fused,ce,nccl")
-    ap.add_argument("--transport", default="push", choices=["push", "pull"], help="fused mode: gather warps store the own shard to every peer (push) or load the peers' shards (pull)")
+    ap.add_argument("--transport", default="pull", choices=["push", "pull"], help="fused mode: gather warps store the own shard to every peer (push) or load the peers' shards (pull)")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--cta-group", type=int, default=2)

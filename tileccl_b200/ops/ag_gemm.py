@@ -5,7 +5,12 @@ K]; the result on every rank is ``concat_r(A_r) @ Bt.T`` = [M, N_local].  The
 shard lives inside the rank's gathered buffer (symmetric heap), so the local
 part needs no copy; gather warps of the GEMM kernel pull the peers' shards with
 P2P loads and the TMA producer starts on a row block as soon as its counter
-says it has landed.  ``gather_rows`` is the granularity of those counters.
+says it has landed.  ``gather_rows`` is the granularity of those counters,
+``item_rows`` the rows one gather warp moves at a time (one row by default, so
+that rows land progressively in the order the tile schedule consumes them).
+``transport="push"`` makes every rank store its shard into all peers' buffers
+instead; measured at 8 GPUs it is slower than pull (2.0 ms against 1.38 ms on
+the 32768 x 3584 x 8192 case) and is kept as the measured alternative.
 
 Reference parity: comm_comp/exp2_ag_gemm_granularity.cu:168-300 (the
 segmented-launch + copy-engine pipeline; its chunk count S is this op's
@@ -23,7 +28,7 @@ from ._plan import Plan, require_bf16_rowmajor
 class AgGemm:
     def __init__(self, heap: SymmetricHeap, M: int, K: int, Bt: torch.Tensor, cta_group: int = 2,
                  gather_rows: int = 512, out: torch.Tensor | None = None, group_m: int = 0,
-                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "push", item_rows: int = 1):
+                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "pull", item_rows: int = 1):
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
         world, rank = heap.world, heap.rank
