@@ -160,6 +160,9 @@ def plan(n_gpus: int, quick: bool, out: Path) -> list[tuple[str, list[str], floa
                                              "--iters", it, "--verify", "--csv", f"{o}/exp3_epilogue.csv"], 900, 2))
     steps.append(("exp2_ag_gemm", launch + ["exp2_ag_gemm_granularity", "--m", "32768", "--k", "8192", "--n-global", "28672", "--gather-rows", "512,4096" if quick else "128,512,2048,4096",
                                             "--iters", "10" if quick else "30", "--verify", "--csv", f"{o}/exp2.csv"], 1200, 2))
+    steps.append(("nvls_bw", launch + ["nvls_bw", "--csv", f"{o}/nvls_bw.csv"] + (["--sizes", "64K,16M,256M", "--iters", "10"] if quick else []), 600, 2))
+    steps.append(("exp3_fused_nvls", launch + ["exp3_gemm_rs_fused", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it, "--transport", "nvls", "--verify",
+                                                "--csv", f"{o}/exp3_fused_nvls.csv"], 600, 2))
     steps.append(("mlp_e2e", launch + ["mlp_e2e", "--iters", "10" if quick else "50", "--verify", "--csv", f"{o}/mlp_e2e.csv"], 900, 1))
     steps.append(("bench", [py, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={max(1, n_gpus)}", "--master-addr", "127.0.0.1", "--master-port", "29571",
                             "bench.py", "--gpus", str(max(1, n_gpus)), "--steps", "10" if quick else "30", "--warmup", "5"], 900, 1))

@@ -6,13 +6,15 @@
 //                segments scattered over peers: the epilogue-remote experiment)
 //   kModeGemmRs  GEMM -> reduce-scatter: the epilogue pushes bf16 partial tiles
 //                with 16-byte st.global into the staging slot of the rank that
-//                owns the rows, bumps that rank's per-tile counter with
-//                red.release.sys, and this rank's reduce warps sum the slots
-//                of its own segment as soon as a tile has all its partials
-//   kModeAgGemm  all-gather -> GEMM: gather warps pull the peers' A shards with
-//                16-byte P2P loads into the local gathered A and publish
-//                per-row-block counters; the TMA producer acquires a row
-//                block's counter before it loads tiles from it
+//                owns the rows; a signalling warp fences at system scope and
+//                bumps the owner's per-tile counter; this rank's reduce warps
+//                sum the slots of its own segment in fp32 as soon as a tile has
+//                all its partials (or, NVLS variant, read the sum through the
+//                NVSwitch with multimem.ld_reduce)
+//   kModeAgGemm  all-gather -> GEMM: gather warps pull the peers' A shards row
+//                by row with 16-byte P2P loads into the local gathered A and
+//                publish per-row-block counters; the TMA producer acquires a
+//                row block's counter before it loads tiles from it
 //
 // A is [M, K] row-major, B is [N, K] row-major (the "column-major B[K, N]" of
 // the reference), D is row-major.  fp32 accumulation, bf16 output.
