@@ -24,3 +24,12 @@ def test_fused_ops_multi_gpu(native_lib, world):
         pytest.skip(f"needs {world} GPUs")
     r = _run(world, 29600 + world)
     assert r.returncode == 0 and "WORKER_OK" in r.stdout, r.stdout[-4000:] + r.stderr[-4000:]
+
+
+def test_native_launcher_driver_two_gpus(native_lib):
+    """The C++ driver: ranks forked by the native launcher, cudaIpc exchange through its shared blob."""
+    from tileccl_b200 import _build
+    exe = str(_build.build(programs=True)["exp3_gemm_rs_fused"])
+    r = subprocess.run([exe, "--ndev", "2", "--m", "2048", "--n", "1024", "--k", "512", "--iters", "5", "--warmup", "2", "--verify"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "FAIL" not in r.stdout and "max over ranks" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -50,6 +50,7 @@ PROGRAMS: dict[str, tuple[list[str], list[str]]] = {
     "intra_sm_matrix": (["bench/intra_sm_matrix.cu"], []),
     "ce_gemm_overlap": (["bench/ce_gemm_overlap.cu"], ["-lcublas"]),
     "exp1_ce_interference": (["bench/exp1_ce_interference.cu"], ["-L", str(LIB_DIR), "-ltileccl", "-Xlinker", "-rpath=$ORIGIN/../lib"]),
+    "exp3_gemm_rs_fused": (["bench/exp3_gemm_rs_fused.cu", "runtime/launcher.cpp"], ["-L", str(LIB_DIR), "-ltileccl", "-Xlinker", "-rpath=$ORIGIN/../lib"]),
     "launcher_selftest": (["bench/launcher_selftest.cpp", "runtime/launcher.cpp"], []),
 }
 
