@@ -214,10 +214,17 @@ def main(argv=None) -> int:
     ap.add_argument("--only", default=None, help="comma list of step-name prefixes")
     ap.add_argument("--list", action="store_true")
     ap.add_argument("--keep", action="store_true", help="do not zip the bundle")
+    ap.add_argument("--ncu", action="store_true", help="also capture the NVLink section of one peer_l2_probe launch with ncu (off by default; needs profiling permission)")
     args = ap.parse_args(argv)
     out = Path(args.resume or args.out or f"reports/results_{time.strftime('%Y%m%d_%H%M%S')}").resolve()
     n = gpu_count()
     steps = plan(n, args.quick, out)
+    if args.ncu and shutil.which("ncu"):
+        # One small single-launch capture, one GPU's kernel, clocks left alone.  The plain command runs first.
+        once = [str(BIN / "peer_l2_probe"), "--modes", "once", "--targets", "peer", "--sizes", "256M", "--total", "1G", "--no-verify"]
+        steps.append(("l2_once_plain", once, 120, 2))
+        steps.append(("l2_once_ncu", ["ncu", "--section", "Nvlink", "--section", "MemoryWorkloadAnalysis", "--clock-control", "none", "-k", "regex:stream_read",
+                                      "-c", "1", "-o", f"{out}/l2_once", "-f"] + once, 300, 2))
     if args.only:
         pre = [p.strip() for p in args.only.split(",")]
         steps = [s for s in steps if any(s[0].startswith(p) for p in pre)]
