@@ -137,8 +137,8 @@ def main():
     xf = torch.cat(gather(x), 0).float()
     f = ffn // world
     parts = []
-    for wgu, wd in zip(gather(mlp.w_gate_up), gather(mlp.w_down)):
-        h = (xf @ wgu.float().t()).bfloat16().float()
+    for wgu, wd in zip(gather(mlp.gate_up_plain()), gather(mlp.w_down)):
+        h = xf @ wgu.float().t()                      # the fused epilogue applies SiLU*mul on the fp32 accumulators
         a = (torch.nn.functional.silu(h[:, :f]) * h[:, f:]).bfloat16().float()
         parts.append(a @ wd.float().t())
     ref = sum(parts)[rank * (tokens // world):(rank + 1) * (tokens // world)]

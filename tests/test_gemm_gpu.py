@@ -149,3 +149,23 @@ def test_elementwise_kernels(native_lib):
     got = (ref32 + 0.01).bfloat16()
     want = ((got.float() - ref32).abs() / (ref32.abs() + 1)).max().item()
     assert abs(ew.max_rel_err(got, ref32) - want) < 1e-6
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_fused_silu_mul_epilogue(native_lib, cta_group):
+    """silu(x @ Wg.T) * (x @ Wu.T) straight from the accumulators, gate/up rows interleaved per tile."""
+    from tileccl_b200.ops.gemm import GemmPlan, deinterleave_gate_up, interleave_gate_up
+    torch.manual_seed(9)
+    M, F, K = 512, 384, 320
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    wg = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.1
+    wu = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.1
+    w = interleave_gate_up(wg, wu)
+    g2, u2 = deinterleave_gate_up(w)
+    assert torch.equal(g2, wg) and torch.equal(u2, wu)
+    plan = GemmPlan(x, w, cta_group=cta_group, epi="silu_mul", timeout_ms=1000)
+    out = plan()
+    plan.check()
+    assert out.shape == (M, F)
+    ref = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+    assert _rel(out, ref) < 1e-2

@@ -61,6 +61,7 @@ class GemmDesc(C.Structure):
         ("rs_mc_stage", C.c_void_p),
         ("range_lo", C.c_uint64 * MAX_WORLD),
         ("range_hi", C.c_uint64 * MAX_WORLD),
+        ("epi_silu_mul", C.c_int32),
         ("ablate", C.c_int32),
     ]
 

@@ -31,6 +31,7 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--cta-group", type=int, default=2)
     ap.add_argument("--gather-rows", type=int, default=512)
+    ap.add_argument("--no-fuse-silu", action="store_true", help="keep SiLU*mul as its own kernel")
     ap.add_argument("--verify", action="store_true")
     ap.add_argument("--csv", default=None)
     args = ap.parse_args(argv)
@@ -39,12 +40,13 @@ def main(argv=None) -> int:
     f = F // world
     dev = torch.device("cuda", torch.cuda.current_device())
     heap = SymmetricHeap(heap_bytes(T, H, F, world) + (64 << 20))
-    mlp = TpMlp(heap, T, H, F, cta_group=args.cta_group, gather_rows=args.gather_rows)
+    mlp = TpMlp(heap, T, H, F, cta_group=args.cta_group, gather_rows=args.gather_rows, fuse_silu=not args.no_fuse_silu)
     x = torch.empty(T // world, H, dtype=torch.bfloat16, device=dev)
     ew.fill_normal_(x, seed=77 + rank)
     mlp.x_shard.copy_(x)
     bar = ew.DeviceBarrier(heap)
     flush = L2Flusher()
+    w_gu_plain = mlp.gate_up_plain()      # the baseline uses the plain gate|up layout and the stand-alone SiLU*mul kernel
     # baseline buffers
     xg = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
     hb = torch.empty(T, 2 * f, dtype=torch.bfloat16, device=dev)
@@ -58,7 +60,7 @@ def main(argv=None) -> int:
             src = xg
         else:
             src = x
-        torch.matmul(src, mlp.w_gate_up.t(), out=hb)
+        torch.matmul(src, w_gu_plain.t(), out=hb)
         ew.silu_mul(hb, ab)
         torch.matmul(ab, mlp.w_down.t(), out=yb_full)
         if world > 1:
@@ -78,7 +80,7 @@ def main(argv=None) -> int:
     ser = C.timed_interleaved({"fused": mlp, "nccl": baseline}, args.iters, args.warmup, before=bar, flush=flush)
     mlp.check()
     # stage breakdown of the fused path
-    parts = C.timed_interleaved({"ag": mlp.ag, "silu": lambda: ew.silu_mul(mlp.h, mlp.act), "rs": mlp.rs},
+    parts = C.timed_interleaved({"ag": mlp.ag, "silu": lambda: ew.silu_mul(hb, ab), "rs": mlp.rs},
                                 max(5, args.iters // 3), 2, before=bar, flush=flush)
     mine = {k: C.stats_of(v) for k, v in {**ser, **parts}.items()}
     allr = G.all_gather_object({k: (s.mean, s.p95) for k, s in mine.items()} | {"rel": max_rel})
@@ -90,7 +92,7 @@ def main(argv=None) -> int:
         roof = r_ag["roofline_us"] + r_rs["roofline_us"] + T * f * 2 * 3 / (roofline.peaks()["hbm_gbs"] * 1e9) * 1e6
         rel = max(r["rel"] for r in allr) if args.verify else float("nan")
         print(f"# mlp_e2e tokens={T} hidden={H} ffn={F} tp={world} cta_group={args.cta_group} [{C.device_line()}]")
-        print(f"fused {fused:.1f} us (p95 {mx('fused', 1):.1f}) = AG+GEMM {mx('ag'):.1f} + SiLU*mul {mx('silu'):.1f} + GEMM+RS {mx('rs'):.1f} (stages timed alone)")
+        print(f"fused {fused:.1f} us (p95 {mx('fused', 1):.1f}) = AG+GEMM{"+SiLU*mul" if mlp.fuse_silu else ""} {mx('ag'):.1f} + GEMM+RS {mx('rs'):.1f} (stages timed alone; stand-alone SiLU*mul kernel: {mx('silu'):.1f})")
         print(f"nccl+cublas {nccl:.1f} us | speedup {nccl / fused:.3f}x | roofline {roof:.1f} us ({100 * roof / fused:.1f} % of {r_ag['peaks']} peaks) | max rel diff {rel:.3g}")
         csv = csvio.CsvAppender(args.csv, csvio.MLP_E2E_COLUMNS)
         csv.row(tokens=T, hidden=H, ffn=F, world=world, fused_us=fused, fused_p95=mx("fused", 1), ag_us=mx("ag"), silu_us=mx("silu"),

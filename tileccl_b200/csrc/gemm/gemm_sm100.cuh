@@ -84,6 +84,7 @@ struct GemmParams {
   int world, rank;
   int epoch;      // 1-based call number of the plan that owns the flag buffers
   int comm_enabled;
+  int epi_silu_mul;  // epilogue computes silu(gate) * up from the two 128-column halves of every tile; D is [M, N/2]
   int ablate;     // experiment knobs (timing only): bit 0 = no reduce warps, bit 1 = no tile signals,
                   // bit 2 = AG+GEMM producer does not wait for gathered rows
 
@@ -153,6 +154,12 @@ struct GemmCfg {
 };
 
 namespace detail {
+
+// epoch * count in wrapping (unsigned) arithmetic: counters are compared by signed distance, so a
+// long-lived plan may let them wrap.
+__device__ __forceinline__ int epoch_times(int epoch, int count) {
+  return static_cast<int>(static_cast<unsigned>(epoch) * static_cast<unsigned>(count));
+}
 
 __device__ __forceinline__ void report(const GemmParams& p, volatile int* s_abort, int code, int d0,
                                        int d1) {
@@ -316,7 +323,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   tc_fence_after_sync();
   const uint32_t tmem_base = *s_tmem_ptr;
-  const int barrier_target = p.epoch * p.world;
+  const int barrier_target = detail::epoch_times(p.epoch, p.world);
 
   // ---- roles ----------------------------------------------------------------
   if (warp == 0) {
@@ -332,7 +339,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (p.mode == kModeAgGemm && fused_comm && !(p.ablate & 4) && (m0 / p.seg_rows) != p.rank) {
           // Rows [m0, m0+BM) lie in one gather block (gather_rows % BM == 0).
           const int blk = m0 / p.gather_rows;
-          const int target = p.epoch * (p.gather_rows / p.ag_item_rows);
+          const int target = detail::epoch_times(p.epoch, p.gather_rows / p.ag_item_rows);
           int seen = 0;
           const bool landed = p.ag_push ? wait_ge<true>(p.ag_flags + blk, target, s_abort, deadline, &seen)
                                         : wait_ge<false>(p.ag_flags + blk, target, s_abort, deadline, &seen);
@@ -437,7 +444,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int b = lt & 1;
       const int row0 = m_blk * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BM;  // first row of this CTA's half
       const int seg = row0 / p.seg_rows;
-      const int col0 = n_blk * Cfg::BN;
+      const int col0 = p.epi_silu_mul ? n_blk * (Cfg::BN / 2) : n_blk * Cfg::BN;   // first output column of the tile
       __nv_bfloat16* dst0 = p.dst_base[seg] +
                             (p.dst_row_off[seg] + row0 - static_cast<long long>(seg) * p.seg_rows) * p.ldc +
                             col0;
@@ -471,6 +478,51 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(b * Cfg::BN);
+      if (p.epi_silu_mul) {
+        // Gate columns [0,128) and up columns [128,256) of the tile belong to the same 128 features:
+        // 32 features at a time, out = silu(gate) * up, into the 256-byte rows of the warp's buffer.
+#pragma unroll 1
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32b_x32(t_row + c4 * 32, g);
+          tmem_ld_32x32b_x32(t_row + Cfg::BN / 2 + c4 * 32, u);
+          tmem_ld_wait();
+          if (c4 == 3) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (kCtaGroup == 1) mbar_arrive(bar_tempty + 8 * b);
+              else mbar_arrive_cluster(mapa(bar_tempty + 8 * b, 0));
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float gv = __uint_as_float(g[8 * j + e]);
+              o[e] = __float_as_uint(gv / (1.f + __expf(-gv)) * __uint_as_float(u[8 * j + e]));
+            }
+            uint4 w;
+            w.x = pack_bf16x2(o[0], o[1]);
+            w.y = pack_bf16x2(o[2], o[3]);
+            w.z = pack_bf16x2(o[4], o[5]);
+            w.w = pack_bf16x2(o[6], o[7]);
+            sts_v4(my_buf + lane * 256 + (((c4 * 4 + j) ^ (lane & 7)) << 4), w);
+          }
+        }
+        __syncwarp();
+        const int ch = lane & 15;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int r = i * 2 + (lane >> 4);
+          const uint4 w = lds_v4(my_buf + r * 256 + ((ch ^ (r & 7)) << 4));
+          if (row0 + q * 32 + r < p.M && col0 + ch * 8 < p.N / 2)
+            st_v4(dst0 + static_cast<long long>(q * 32 + r) * p.ldc + ch * 8, w);
+        }
+        __syncwarp();
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < Cfg::BN / Cfg::EPI_CHUNK_COLS; ++c) {
         uint32_t v0[32], v1[32];
@@ -546,7 +598,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // ---- reduce warps: sum the `world` staged partials of each tile of this
       // rank's segment, in the order in which the producers complete them ----
       const int items = (p.seg_rows / Cfg::BM) * sched.n_tiles;
-      const int target = p.epoch * p.world;
+      const int target = detail::epoch_times(p.epoch, p.world);
       const size_t slot_elems = static_cast<size_t>(p.seg_rows) * p.N;
       for (int j = blockIdx.x; j < items; j += gridDim.x) {
         if (ctid == 0) {
@@ -683,7 +735,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // the last gather warp of the grid sends one signal per peer.
         if (lane == 0) {
           const int done = atom_add_acq_rel_gpu(p.ag_done, 1) + 1;
-          if (done == p.epoch * n_gw) {
+          if (done == detail::epoch_times(p.epoch, n_gw)) {
             for (int s = 0; s < p.world; ++s)
               if (s != p.rank) red_release_sys_add(p.ag_read_done[s], 1);
           }
@@ -692,8 +744,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // this rank's shard, so the caller may overwrite it after the kernel.
         if (blockIdx.x == 0 && cw == 0 && lane == 0) {
           int seen = 0;
-          if (!wait_ge<true>(p.ag_read_done[p.rank], p.epoch * (p.world - 1), s_abort, deadline, &seen, 512)) {
-            detail::report(p, s_abort, kErrAgEndBarrier, p.epoch * (p.world - 1), seen);
+          if (!wait_ge<true>(p.ag_read_done[p.rank], detail::epoch_times(p.epoch, p.world - 1), s_abort, deadline, &seen, 512)) {
+            detail::report(p, s_abort, kErrAgEndBarrier, detail::epoch_times(p.epoch, p.world - 1), seen);
           }
         }
       }

@@ -68,10 +68,11 @@ __global__ void barrier_all_kernel(BarrierArgs a, int world, int rank, int epoch
   if (lane == 0) {
     const unsigned long long deadline = ptx::globaltimer_ns() + timeout_ns;
     int seen = 0;
-    if (!ptx::wait_ge<true>(a.counters[rank], epoch * world, nullptr, deadline, &seen)) {
+    const int target = static_cast<int>(static_cast<unsigned>(epoch) * static_cast<unsigned>(world));  // may wrap
+    if (!ptx::wait_ge<true>(a.counters[rank], target, nullptr, deadline, &seen)) {
       if (atomicCAS(status, 0, kErrStartBarrier) == 0) {
         status[1] = rank;
-        status[2] = epoch * world;
+        status[2] = target;
         status[3] = seen;
       }
     }
@@ -239,6 +240,8 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
   p.world = d->world; p.rank = d->rank;
   p.comm_enabled = d->comm_enabled;
   p.ablate = d->ablate;
+  p.epi_silu_mul = d->epi_silu_mul;
+  if (d->epi_silu_mul && d->mode == TCL_MODE_GEMM_RS) { set_err(err, errlen, "epi_silu_mul is not available for GEMM+RS"); delete pl; return nullptr; }
   p.seg_rows = d->seg_rows;
   for (int s = 0; s < TCL_MAX_WORLD; ++s) {
     p.dst_base[s] = static_cast<__nv_bfloat16*>(d->dst_base[s]);

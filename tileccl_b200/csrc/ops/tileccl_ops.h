@@ -58,6 +58,8 @@ typedef struct tcl_gemm_desc {
   const void* rs_mc_stage; /* GEMM+RS NVLS variant: multicast mapping of the [M][N] staging buffer, else NULL */
   uint64_t range_lo[TCL_MAX_WORLD]; /* debug build: mapped range of the memory of rank s that this plan may touch */
   uint64_t range_hi[TCL_MAX_WORLD];
+  int32_t epi_silu_mul; /* plain / AG+GEMM: every 256-column tile holds 128 gate columns then the 128 up columns of the same
+                           features; the epilogue writes silu(gate) * up: D is [M, N/2] (ldc is its pitch) */
   int32_t ablate;       /* experiments only: bit 0 = no reduce warps, bit 1 = no tile signals */
 } tcl_gemm_desc;
 

@@ -4,8 +4,11 @@ sequence-sharded activations in and out:
     x_shard [T/tp, H] --AG+GEMM(gate|up)--> [T, 2F/tp] --SiLU*mul--> [T, F/tp]
                       --GEMM+RS(down)----> y_shard [T/tp, H]
 
-Three kernel launches per forward: the fused all-gather GEMM, the fused
-SiLU*mul, the fused GEMM reduce-scatter.  The reference has no model; this is
+Two kernel launches per forward: the all-gather GEMM, whose epilogue applies
+SiLU(gate) * up on the accumulators (gate and up rows of the weight are
+interleaved in 128-row blocks so that every output tile holds matching
+columns), and the GEMM reduce-scatter.  ``fuse_silu=False`` keeps the
+stand-alone SiLU*mul kernel between them (three launches).  The reference has no model; this is
 the end-to-end pipeline named by the benchmark configuration (hidden 8192, ffn
 28672, 16384 tokens, tp = 8).
 """
@@ -30,7 +33,8 @@ def heap_bytes(tokens: int, hidden: int, ffn: int, world: int) -> int:
 
 class TpMlp:
     def __init__(self, heap: SymmetricHeap, tokens: int, hidden: int = 8192, ffn: int = 28672,
-                 cta_group: int = 2, gather_rows: int = 512, seed: int = 0, init_std: float = 0.02):
+                 cta_group: int = 2, gather_rows: int = 512, seed: int = 0, init_std: float = 0.02,
+                 fuse_silu: bool = True):
         world, rank = heap.world, heap.rank
         if ffn % world or tokens % world:
             raise ValueError("ffn and tokens must be divisible by the world size")
@@ -38,14 +42,22 @@ class TpMlp:
         self.tokens, self.hidden, self.ffn_local = tokens, hidden, f
         dev = torch.device("cuda", torch.cuda.current_device())
         # Weights in the K-major layout the kernels take: [out_features, in_features].
-        self.w_gate_up = torch.empty(2 * f, hidden, dtype=torch.bfloat16, device=dev)   # rows: gate | up
+        # w_gate_up rows: fuse_silu -> 128 gate rows, 128 up rows, 128 gate rows, ... (interleave_gate_up);
+        # otherwise all gate rows, then all up rows.
+        self.fuse_silu = fuse_silu and f % 128 == 0
+        self.w_gate_up = torch.empty(2 * f, hidden, dtype=torch.bfloat16, device=dev)
         self.w_down = torch.empty(hidden, f, dtype=torch.bfloat16, device=dev)
         ew.fill_normal_(self.w_gate_up, seed=seed * 1000 + 2 * rank, std=init_std)
         ew.fill_normal_(self.w_down, seed=seed * 1000 + 2 * rank + 1, std=init_std)
-        self.h = torch.empty(tokens, 2 * f, dtype=torch.bfloat16, device=dev)
         self.act = torch.empty(tokens, f, dtype=torch.bfloat16, device=dev)
-        self.ag = AgGemm(heap, tokens, hidden, self.w_gate_up, cta_group=cta_group,
-                         gather_rows=gather_rows, out=self.h)
+        if self.fuse_silu:
+            self.h = None
+            self.ag = AgGemm(heap, tokens, hidden, self.w_gate_up, cta_group=cta_group,
+                             gather_rows=gather_rows, out=self.act, epi="silu_mul")
+        else:
+            self.h = torch.empty(tokens, 2 * f, dtype=torch.bfloat16, device=dev)
+            self.ag = AgGemm(heap, tokens, hidden, self.w_gate_up, cta_group=cta_group,
+                             gather_rows=gather_rows, out=self.h)
         self.rs = GemmRs(heap, self.act, self.w_down, cta_group=cta_group)
 
     @property
@@ -55,7 +67,8 @@ class TpMlp:
 
     def forward(self, stream=None) -> torch.Tensor:
         self.ag(stream)
-        ew.silu_mul(self.h, self.act, stream)
+        if not self.fuse_silu:
+            ew.silu_mul(self.h, self.act, stream)
         return self.rs(stream)
 
     __call__ = forward
@@ -64,6 +77,14 @@ class TpMlp:
         self.ag.check()
         self.rs.check()
 
+    def gate_up_plain(self) -> torch.Tensor:
+        """The gate|up weight in the plain layout (all gate rows, then all up rows)."""
+        if not self.fuse_silu:
+            return self.w_gate_up
+        from ..ops.gemm import deinterleave_gate_up
+        g, u = deinterleave_gate_up(self.w_gate_up)
+        return torch.cat([g, u], 0).contiguous()
+
     @property
     def launches(self) -> int:
-        return self.ag.launches + self.rs.launches + self.ag.launches  # ag, silu_mul (one per forward), rs
+        return self.ag.launches + self.rs.launches + (0 if self.fuse_silu else self.ag.launches)

@@ -28,7 +28,7 @@ from ._plan import Plan, require_bf16_rowmajor
 class AgGemm:
     def __init__(self, heap: SymmetricHeap, M: int, K: int, Bt: torch.Tensor, cta_group: int = 2,
                  gather_rows: int = 512, out: torch.Tensor | None = None, group_m: int = 0,
-                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "pull", item_rows: int = 1):
+                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "pull", item_rows: int = 1, epi: str | None = None):
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
         world, rank = heap.world, heap.rank
@@ -47,8 +47,13 @@ class AgGemm:
         self.done = heap.zeros((32,), torch.int32)       # [0] gather warps done, [16] peers done reading
         self.barrier = heap.zeros((32,), torch.int32)
         self.a_shard = self.a_full[rank * seg:(rank + 1) * seg]
+        if epi not in (None, "silu_mul"):
+            raise ValueError("epi must be None or 'silu_mul'")
+        n_out = N // 2 if epi == "silu_mul" else N      # silu_mul: Bt in the interleave_gate_up layout
         if out is None:
-            out = torch.empty(M, N, dtype=torch.bfloat16, device=Bt.device)
+            out = torch.empty(M, n_out, dtype=torch.bfloat16, device=Bt.device)
+        if tuple(out.shape) != (M, n_out):
+            raise ValueError(f"out must be [{M}, {n_out}]")
         self.out = out
         d = _native.GemmDesc()
         d.mode, d.cta_group = _native.MODE_AG_GEMM, cta_group
@@ -70,6 +75,7 @@ class AgGemm:
             d.ag_dst[s] = heap.peer_ptr(self.a_full, s)
             d.ag_flag_peer[s] = heap.peer_ptr(self.flags, s)
         d.ag_push = 1 if transport == "push" else 0
+        d.epi_silu_mul = 1 if epi == "silu_mul" else 0
         d.ag_flags = self.flags.data_ptr()
         for s in range(world):   # debug build: the only memory of rank s this plan may touch is its heap
             d.range_lo[s] = heap.base[s]

@@ -15,7 +15,7 @@ from ._plan import Plan, require_bf16_rowmajor
 class GemmPlan(Plan):
     def __init__(self, A: torch.Tensor, Bt: torch.Tensor, out: torch.Tensor | None = None,
                  cta_group: int = 2, group_m: int = 0, num_ctas: int = 0, timeout_ms: float = 4000.0,
-                 dst_ptrs: list[int] | None = None, seg_rows: int | None = None):
+                 dst_ptrs: list[int] | None = None, seg_rows: int | None = None, epi: str | None = None):
         """``dst_ptrs``/``seg_rows`` route row segments of D to other addresses
         (a peer's buffer): the epilogue-remote experiment."""
         require_bf16_rowmajor(A, "A")
@@ -24,8 +24,13 @@ class GemmPlan(Plan):
         N, K2 = Bt.shape
         if K2 != K:
             raise ValueError("A is [M, K] and Bt is [N, K]: K differs")
+        if epi not in (None, "silu_mul"):
+            raise ValueError("epi must be None or 'silu_mul'")
+        n_out = N // 2 if epi == "silu_mul" else N
         if out is None:
-            out = torch.empty(M, N, dtype=torch.bfloat16, device=A.device)
+            out = torch.empty(M, n_out, dtype=torch.bfloat16, device=A.device)
+        if out.shape != (M, n_out):
+            raise ValueError(f"out must be [{M}, {n_out}]")
         require_bf16_rowmajor(out, "out")
         d = _native.GemmDesc()
         d.mode, d.cta_group = _native.MODE_PLAIN, cta_group
@@ -41,12 +46,30 @@ class GemmPlan(Plan):
             d.dst_row_off[s] = 0 if dst_ptrs else s * d.seg_rows
         d.timeout_ns = int(timeout_ms * 1e6)
         d.group_m, d.num_ctas = group_m, num_ctas
+        d.epi_silu_mul = 1 if epi == "silu_mul" else 0
         super().__init__(d, keep_alive=(A, Bt, out))
         self.out = out
 
     def __call__(self, stream=None) -> torch.Tensor:
         self.run(stream)
         return self.out
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[F, K] gate and up weights -> one [2F, K] weight whose 256-row blocks hold 128 gate rows
+    followed by the 128 up rows of the same features: the layout the ``silu_mul`` epilogue expects
+    (every 256-column output tile then carries matching gate and up columns).  F % 128 == 0."""
+    F, K = w_gate.shape
+    if w_up.shape != (F, K) or F % 128:
+        raise ValueError("gate and up must both be [F, K] with F a multiple of 128")
+    return torch.stack([w_gate.view(F // 128, 128, K), w_up.view(F // 128, 128, K)], dim=1).reshape(2 * F, K).contiguous()
+
+
+def deinterleave_gate_up(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Inverse of :func:`interleave_gate_up`."""
+    two_f, K = w.shape
+    v = w.view(two_f // 256, 2, 128, K)
+    return v[:, 0].reshape(two_f // 2, K), v[:, 1].reshape(two_f // 2, K)
 
 
 def gemm(A: torch.Tensor, Bt: torch.Tensor, cta_group: int = 2) -> torch.Tensor:
