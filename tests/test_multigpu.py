@@ -33,3 +33,14 @@ def test_native_launcher_driver_two_gpus(native_lib):
     r = subprocess.run([exe, "--ndev", "2", "--m", "2048", "--n", "1024", "--k", "512", "--iters", "5", "--warmup", "2", "--verify"],
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "FAIL" not in r.stdout and "max over ranks" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_native_exp2_and_epilogue_drivers_two_gpus(native_lib):
+    from tileccl_b200 import _build
+    outs = _build.build(programs=True)
+    r = subprocess.run([str(outs["exp2_ag_gemm_granularity"]), "--ndev", "2", "--m", "2048", "--k", "512", "--n", "512", "--gather-rows", "256,1024",
+                        "--iters", "3", "--warmup", "1", "--verify"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "FAIL" not in r.stdout and r.stdout.count(" ok") == 2, r.stdout[-3000:] + r.stderr[-3000:]
+    r = subprocess.run([str(outs["exp3_epilogue_remote"]), "--ndev", "2", "--sizes", "1024x512x256", "--iters", "3", "--warmup", "1", "--verify"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "FAIL" not in r.stdout and r.stdout.count(" ok") == 3, r.stdout[-3000:] + r.stderr[-3000:]

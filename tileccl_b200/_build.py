@@ -51,6 +51,8 @@ PROGRAMS: dict[str, tuple[list[str], list[str]]] = {
     "ce_gemm_overlap": (["bench/ce_gemm_overlap.cu"], ["-lcublas"]),
     "exp1_ce_interference": (["bench/exp1_ce_interference.cu"], ["-L", str(LIB_DIR), "-ltileccl", "-Xlinker", "-rpath=$ORIGIN/../lib"]),
     "exp3_gemm_rs_fused": (["bench/exp3_gemm_rs_fused.cu", "runtime/launcher.cpp"], ["-L", str(LIB_DIR), "-ltileccl", "-Xlinker", "-rpath=$ORIGIN/../lib"]),
+    "exp2_ag_gemm_granularity": (["bench/exp2_ag_gemm_granularity.cu", "runtime/launcher.cpp"], ["-L", str(LIB_DIR), "-ltileccl", "-Xlinker", "-rpath=$ORIGIN/../lib"]),
+    "exp3_epilogue_remote": (["bench/exp3_epilogue_remote.cu", "runtime/launcher.cpp"], ["-L", str(LIB_DIR), "-ltileccl", "-Xlinker", "-rpath=$ORIGIN/../lib"]),
     "launcher_selftest": (["bench/launcher_selftest.cpp", "runtime/launcher.cpp"], []),
 }
 

@@ -169,6 +169,8 @@ def plan(n_gpus: int, quick: bool, out: Path) -> list[tuple[str, list[str], floa
     # ---- C++ programs (single process, several GPUs) ----
     b = lambda n: str(BIN / n)  # noqa: E731
     steps.append(("exp3_fused_native", [b("exp3_gemm_rs_fused"), "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it, "--verify", "--csv", f"{o}/exp3_fused_native.csv"], 600, 2))
+    steps.append(("exp2_native", [b("exp2_ag_gemm_granularity"), "--gather-rows", "512,4096" if quick else "128,512,2048,4096", "--iters", "8" if quick else "30", "--verify", "--csv", f"{o}/exp2_native.csv"], 900, 2))
+    steps.append(("exp3_epilogue_native", [b("exp3_epilogue_remote"), "--iters", it, "--verify", "--csv", f"{o}/exp3_epilogue_native.csv"], 600, 2))
     steps.append(("exp1_ce_interference", [b("exp1_ce_interference"), "--sizes", "8192" if quick else "2048,4096,8192", "--iters", "10" if quick else "30", "--csv", f"{o}/exp1.csv"], 900, 2))
     steps.append(("pk_bw_sweep", [b("pk_bw_sweep"), "--total", "256M" if quick else "1G", "--csv", f"{o}/pk_bw.csv"], 900, 2))
     steps.append(("p2p_ce_vs_tma", [b("p2p_ce_vs_tma"), "--csv", f"{o}/p2p_ce_vs_tma.csv"] + (["--tokens", "1,64,4096", "--iters", "20"] if quick else []), 600, 2))
