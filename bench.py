@@ -64,7 +64,7 @@ def main():
     from tileccl_b200.parallel import group as G
     from tileccl_b200.parallel.heap import SymmetricHeap
     from tileccl_b200.utils import roofline
-    from tileccl_b200.utils.clocks import ClockSampler
+    from tileccl_b200.utils.clocks import make_sampler
     from tileccl_b200.utils.timing import L2Flusher
 
     if not torch.cuda.is_available():
@@ -74,7 +74,7 @@ def main():
     rank, world, local = G.init()
     # Clock / throttle sampling runs from here to the end of the fused timing;
     # the summary keeps the samples taken under load.
-    sampler = ClockSampler(period_ms=50, gpu_index=local).start() if rank == 0 else None
+    sampler = None            # started right before the timed loop
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE is {world}", file=sys.stderr)
     tp = world
@@ -170,6 +170,10 @@ def main():
     # A run that saw a hardware or thermal slow-down is not a measurement: take it once more.
     bad_reasons = {"hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown"}
     for attempt in range(2):
+        # Clock / throttle sampling (read-only) spans exactly the timed loop of this attempt.
+        if rank == 0:
+            phys = int(os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")[local]) if os.environ.get("CUDA_VISIBLE_DEVICES", "").replace(",", "").isdigit() else local
+            sampler = make_sampler(phys).start()
         launches0 = rs.launches + ag.launches
         res = timed(variants, steps, warmup)
         gpu_launches = rs.launches + ag.launches - launches0 - 2 * warmup
@@ -181,7 +185,6 @@ def main():
             break
         if rank == 0:
             print(f"clock record shows {clocks['reasons']}: measuring once more", file=sys.stderr)
-            sampler = ClockSampler(period_ms=50, gpu_index=local).start()
         time.sleep(2.0)
     if clocks is not None:
         clocks["attempts"] = attempt + 1

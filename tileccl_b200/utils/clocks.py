@@ -60,6 +60,70 @@ class ClockSampler:
         return summarize(rows)
 
 
+class NvmlSampler:
+    """Same record, taken in-process through NVML (read-only queries) by a thread every few
+    milliseconds: fine enough to catch a timed region that lasts a fraction of a second.
+    :func:`make_sampler` falls back to :class:`ClockSampler` when NVML is not importable."""
+
+    # nvmlClocksEventReasons bits
+    _BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
+
+    def __init__(self, period_ms: int = 10, gpu_index: int = 0):
+        import threading
+
+        import pynvml
+        self.n = pynvml
+        pynvml.nvmlInit()
+        self.h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        self.index = gpu_index
+        self.period = period_ms / 1000.0
+        self.rows: list[dict] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+
+    def _loop(self):
+        import time
+        n, h = self.n, self.h
+        try:
+            sm_max = float(n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001
+            sm_max = 0.0
+        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self._stop.is_set():
+            try:
+                mask = int(get_reasons(h))
+                row = {"index": self.index, "sm": float(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)), "sm_max": sm_max,
+                       "power": n.nvmlDeviceGetPowerUsage(h) / 1000.0, "active": hex(mask),
+                       "hw_slowdown": "Active" if mask & 0x8 else "Not Active", "hw_thermal": "Active" if mask & 0x40 else "Not Active",
+                       "sw_thermal": "Active" if mask & 0x20 else "Not Active", "sw_power_cap": "Active" if mask & 0x4 else "Not Active"}
+                self.rows.append(row)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(self.period)
+
+    def start(self) -> "NvmlSampler":
+        self._thread.start()
+        return self
+
+    def stop(self) -> None:
+        self._stop.set()
+        self._thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        self.stop()
+        out = summarize(self.rows)
+        out["source"] = "nvml"
+        return out
+
+
+def make_sampler(gpu_index: int, period_ms: int = 10):
+    """An NVML thread sampler when possible, else the nvidia-smi subprocess sampler."""
+    try:
+        return NvmlSampler(period_ms=period_ms, gpu_index=gpu_index)
+    except Exception:  # noqa: BLE001
+        return ClockSampler(period_ms=max(50, period_ms), gpu_index=gpu_index)
+
+
 def parse_samples(text: str) -> list[dict]:
     rows = []
     for line in text.splitlines():
