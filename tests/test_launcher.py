@@ -26,3 +26,10 @@ def test_launcher_scenarios(selftest, mode, world):
 def test_device_probe_runs_in_a_child(selftest):
     r = subprocess.run([selftest, "--probe-devices"], capture_output=True, text=True, timeout=60)
     assert r.returncode == 0 and r.stdout.startswith("devices:")
+
+
+def test_host_plumbing_selftest(selftest, tmp_path):
+    from tileccl_b200 import _build
+    exe = str(_build.build(programs=True)["host_selftest"])
+    r = subprocess.run([exe, str(tmp_path / "x.csv")], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "PASS" in r.stdout, r.stdout + r.stderr

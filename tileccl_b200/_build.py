@@ -53,6 +53,7 @@ PROGRAMS: dict[str, tuple[list[str], list[str]]] = {
     "exp3_gemm_rs_fused": (["bench/exp3_gemm_rs_fused.cu", "runtime/launcher.cpp"], ["-L", str(LIB_DIR), "-ltileccl", "-Xlinker", "-rpath=$ORIGIN/../lib"]),
     "exp2_ag_gemm_granularity": (["bench/exp2_ag_gemm_granularity.cu", "runtime/launcher.cpp"], ["-L", str(LIB_DIR), "-ltileccl", "-Xlinker", "-rpath=$ORIGIN/../lib"]),
     "exp3_epilogue_remote": (["bench/exp3_epilogue_remote.cu", "runtime/launcher.cpp"], ["-L", str(LIB_DIR), "-ltileccl", "-Xlinker", "-rpath=$ORIGIN/../lib"]),
+    "host_selftest": (["bench/host_selftest.cpp"], []),
     "launcher_selftest": (["bench/launcher_selftest.cpp", "runtime/launcher.cpp"], []),
 }
 
