@@ -3,6 +3,7 @@
 Each check compares a fused op against a plain PyTorch fp32 computation on the
 all-gathered inputs.  Prints ``WORKER_OK`` on rank 0 when every check passed.
 """
+import ctypes as C
 import os
 import sys
 
@@ -123,6 +124,23 @@ def main():
             torch.cuda.synchronize()
             dist.barrier()
         del op
+        # barrier with one multimem.red per rank: a rank may pass only after every rank arrived
+        mbar = ew.DeviceBarrier(mc_heap, timeout_ms=2000, transport="nvls")
+        seen = mc_heap.zeros((4 * world,), torch.int32)   # one 16-byte slot per source rank
+        mine = torch.zeros(4, dtype=torch.int32, device="cuda")
+        lib, vp = _native.lib(), C.c_void_p
+        for ep in range(1, 4):
+            mine.fill_(ep)
+            for r in range(world):   # publish "arrived at ep" on every peer (own copy kernel), then the barrier
+                _native.check(lib.tcl_p2p_copy(vp(mc_heap.peer_ptr(seen, r) + 16 * rank), vp(mine.data_ptr()), 16, 1,
+                                               vp(torch.cuda.current_stream().cuda_stream)), "p2p_copy")
+            mbar()
+            torch.cuda.synchronize()
+            got = seen[::4].tolist()
+            if any(g < ep for g in got):
+                fails.append(f"nvls barrier epoch {ep}: passed before every rank arrived: {got}")
+        mbar.check()
+        dist.barrier()
         mc_heap.close()
 
     # ---- MLP block ----

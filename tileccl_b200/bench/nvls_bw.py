@@ -6,6 +6,8 @@
     mc_ldreduce multimem.ld_reduce: one load returns the sum over all GPUs, added inside the switch
     mc_red      multimem.red: one instruction adds into every GPU's copy
     nccl_ag / nccl_rs   ncclAllGather / ncclReduceScatter of the same payload (baseline)
+    barrier_p2p / barrier_mc   all-ranks device barrier: one red.release per peer, or one multimem.red.release
+                               per rank (bytes = 0; us is the launch-to-exit time of the barrier kernel)
 
 GB/s is payload bytes per rank per second (for nccl_*: the bus-bandwidth convention, (w-1)/w of the
 full buffer).  Needs a symmetric heap on the VMM back end bound to a multicast object; when the
@@ -134,6 +136,15 @@ def main(argv=None) -> int:
             if rank == 0:
                 print(f"{mv:12s} {n:11d} | {us:10.2f} {gbps:9.1f} | {verify}")
                 csv.row(mover=mv, bytes=n, world=world, us=us, gbps=gbps, verify=verify)
+    # barrier latency: world stores per rank against one multicast store per rank
+    flavours = [("barrier_p2p", ew.DeviceBarrier(heap, transport="p2p"))] + ([("barrier_mc", ew.DeviceBarrier(heap, transport="nvls"))] if use_mc else [])
+    for name, b in flavours:
+        us = G.max_over_ranks(C.stats_of(C.timed_series(b, max(args.iters, 50), 5, before=bar)).p50)
+        torch.cuda.synchronize()
+        b.check()
+        if rank == 0:
+            print(f"{name:12s} {0:11d} | {us:10.2f} {'-':>9s} | -")
+            csv.row(mover=name, bytes=0, world=world, us=us, gbps=0.0, verify="-")
     bar.check()
     csv.close()
     torch.cuda.synchronize()

@@ -3,6 +3,7 @@
 //   ld_reduce  every GPU -> local sum    multimem.ld_reduce     (the reduce-scatter building block; the
 //                                                                switch adds the bf16 values in fp32)
 //   red        local -> added everywhere multimem.red
+//   barrier    one multimem.red.release per rank on a counter, instead of one red per peer
 // and a plain peer copy (ld/st through a peer mapping) for comparison.  Simple grid-stride kernels: they
 // are the movers of the NVLS bandwidth sweep, and the in-switch reduce path of the fused GEMM+RS reuses
 // the same instruction wrappers (ptx/ldst_sys.cuh).
@@ -13,6 +14,7 @@
 #include <cstdint>
 
 #include "../ptx/ldst_sys.cuh"
+#include "../ptx/mbarrier.cuh"
 
 namespace {
 using namespace tcl::ptx;
@@ -45,6 +47,25 @@ __global__ void p2p_copy_kernel(uint4* dst, const uint4* __restrict__ src, size_
   for (; i < nvec; i += st) st_v4(dst + i, ld_v4_stream(src + i));
 }
 
+// All-ranks barrier with ONE store per rank: the switch adds 1 to the counter's copy on every GPU.
+// The counter is an epoch counter (never reset): a rank leaves when its own copy reached epoch*world.
+// status = {code, rank, wanted, seen}; code 1 is the same "start barrier timed out" as the peer-store barrier.
+__global__ void barrier_all_mc_kernel(int* mc_counter, const int* local_counter, int world, int rank, int epoch, int* status,
+                                      unsigned long long timeout_ns) {
+  if (threadIdx.x != 0) return;
+  multimem_red_release_add(mc_counter, 1);
+  const unsigned long long deadline = globaltimer_ns() + timeout_ns;
+  int seen = 0;
+  const int target = static_cast<int>(static_cast<unsigned>(epoch) * static_cast<unsigned>(world));  // may wrap
+  if (!wait_ge<true>(local_counter, target, nullptr, deadline, &seen)) {
+    if (atomicCAS(status, 0, 1) == 0) {
+      status[1] = rank;
+      status[2] = target;
+      status[3] = seen;
+    }
+  }
+}
+
 int grid_for(size_t nvec, int blocks) {
   if (blocks > 0) return blocks;
   size_t b = (nvec + 1023) / 1024;
@@ -67,6 +88,13 @@ int tcl_nvls_red(void* mc_dst, const void* src, size_t bytes, int blocks, void* 
 }
 int tcl_p2p_copy(void* dst, const void* src, size_t bytes, int blocks, void* stream) {
   p2p_copy_kernel<<<grid_for(bytes / 16, blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(dst), static_cast<const uint4*>(src), bytes / 16);
+  return static_cast<int>(cudaGetLastError());
+}
+int tcl_barrier_all_mc(int32_t* mc_counter, const int32_t* local_counter, int world, int rank, int epoch, int32_t* status,
+                       uint64_t timeout_ns, void* stream) {
+  if (!mc_counter || !local_counter || world < 1 || rank < 0 || rank >= world) return static_cast<int>(cudaErrorInvalidValue);
+  barrier_all_mc_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(mc_counter, local_counter, world, rank, epoch, status,
+                                                                      timeout_ns ? timeout_ns : 4000000000ull);
   return static_cast<int>(cudaGetLastError());
 }
 }

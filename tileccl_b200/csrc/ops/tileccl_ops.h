@@ -82,6 +82,13 @@ void tcl_sched_tile(int m_tiles, int n_tiles, int group_m, int order, int world,
 int tcl_barrier_all(int32_t* const* counters, int world, int rank, int epoch, int32_t* status,
                     uint64_t timeout_ns, void* stream);
 
+/* The same barrier with one store per rank: a multimem.red.release on the counter's multicast address
+ * adds 1 to every rank's copy inside the switch.  `mc_counter` is the multicast address of a counter in
+ * a multicast-bound symmetric heap, `local_counter` this rank's own copy.  Keep one counter per barrier
+ * flavour: both count epochs.  The reference has no multicast path. */
+int tcl_barrier_all_mc(int32_t* mc_counter, const int32_t* local_counter, int world, int rank, int epoch,
+                       int32_t* status, uint64_t timeout_ns, void* stream);
+
 /* out[r, c] = silu(gu[r, c]) * gu[r, ffn + c]; gu is [rows, 2*ffn] bf16. */
 int tcl_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t ffn, void* stream);
 

@@ -47,18 +47,31 @@ def max_rel_err(got: torch.Tensor, ref_f32: torch.Tensor, stream=None) -> float:
 
 
 class DeviceBarrier:
-    """All-ranks device barrier on a stream (epoch counters, bounded wait)."""
+    """All-ranks device barrier on a stream (epoch counters, bounded wait).
 
-    def __init__(self, heap, timeout_ms: float = 4000.0):
+    ``transport="p2p"``: every rank adds 1 to every rank's counter through the peer mappings (world
+    stores per rank).  ``transport="nvls"``: one ``multimem.red.release`` per rank on the counter's
+    multicast address, the switch fans it out; needs a heap created with ``multicast=True``.
+    """
+
+    def __init__(self, heap, timeout_ms: float = 4000.0, transport: str = "p2p"):
+        if transport not in ("p2p", "nvls"):
+            raise ValueError(f"unknown barrier transport {transport!r}")
         self.heap = heap
+        self.transport = transport
         self.counter = heap.zeros((32,), torch.int32)
         self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
         self.ptrs = (C.c_void_p * _native.MAX_WORLD)(*[heap.peer_ptr(self.counter, r) for r in range(heap.world)])
+        self.mc_ptr = heap.mc_ptr(self.counter) if transport == "nvls" else None
         self.epoch = 0
         self.timeout_ns = int(timeout_ms * 1e6)
 
     def __call__(self, stream=None) -> None:
         self.epoch += 1
+        if self.transport == "nvls":
+            _native.check(_native.lib().tcl_barrier_all_mc(self.mc_ptr, self.counter.data_ptr(), self.heap.world, self.heap.rank, self.epoch,
+                                                           self.status.data_ptr(), self.timeout_ns, _stream_ptr(stream)), "barrier")
+            return
         _native.check(_native.lib().tcl_barrier_all(self.ptrs, self.heap.world, self.heap.rank, self.epoch,
                                                     self.status.data_ptr(), self.timeout_ns, _stream_ptr(stream)), "barrier")
 
