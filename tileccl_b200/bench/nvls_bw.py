@@ -8,6 +8,8 @@
     nccl_ag / nccl_rs   ncclAllGather / ncclReduceScatter of the same payload (baseline)
     barrier_p2p / barrier_mc   all-ranks device barrier: one red.release per peer, or one multimem.red.release
                                per rank (bytes = 0; us is the launch-to-exit time of the barrier kernel)
+    rtt_st_release / rtt_red_release / rtt_mc_red   flag ping-pong between ranks 0 and 1, timed inside the kernel
+                               with %globaltimer: us is one round trip (two signals)
 
 GB/s is payload bytes per rank per second (for nccl_*: the bus-bandwidth convention, (w-1)/w of the
 full buffer).  Needs a symmetric heap on the VMM back end bound to a multicast object; when the
@@ -145,6 +147,30 @@ def main(argv=None) -> int:
         if rank == 0:
             print(f"{name:12s} {0:11d} | {us:10.2f} {'-':>9s} | -")
             csv.row(mover=name, bytes=0, world=world, us=us, gbps=0.0, verify="-")
+    # signal round trip between ranks 0 and 1 (the other ranks idle): plain, reduction and multicast signals
+    if world > 1:
+        rounds = 2000
+        pp_status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        ns = torch.zeros(1, dtype=torch.float32, device="cuda")
+        for mode, name in enumerate(["rtt_st_release", "rtt_red_release", "rtt_mc_red"]):
+            if mode == 2 and not use_mc:
+                continue
+            flag = heap.zeros((32,), torch.int32)
+            torch.cuda.synchronize(); G.host_barrier()
+            base = 0
+            for _ in range(3):   # the first call warms the path; the last one is reported
+                if rank < 2:
+                    remote = heap.mc_ptr(flag) if mode == 2 else heap.peer_ptr(flag, 1 - rank)
+                    _native.check(lib.tcl_signal_pingpong(vp(flag.data_ptr()), vp(remote), mode, 1 if rank == 0 else 0, base, rounds,
+                                                          vp(ns.data_ptr()), vp(pp_status.data_ptr()), 0, st()), name)
+                torch.cuda.synchronize(); G.host_barrier()
+                base += (2 if mode == 2 else 1) * rounds
+            if int(pp_status[0]) != 0:
+                raise RuntimeError(f"{name}: wait ran out: {pp_status.tolist()}")
+            if rank == 0:
+                us = float(ns.item()) / 1e3
+                print(f"{name:15s} {0:8d} | {us:10.3f} {'-':>9s} | -")
+                csv.row(mover=name, bytes=0, world=world, us=us, gbps=0.0, verify="-")
     bar.check()
     csv.close()
     torch.cuda.synchronize()

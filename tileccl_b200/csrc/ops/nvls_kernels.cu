@@ -66,6 +66,40 @@ __global__ void barrier_all_mc_kernel(int* mc_counter, const int* local_counter,
   }
 }
 
+// Flag ping-pong between two ranks (one thread each).  The signal goes out as
+//   mode 0  st.release.sys of the round number to the peer's flag
+//   mode 1  red.release.sys.add of 1 on the peer's flag
+//   mode 2  multimem.red.release.add of 1 on the flag's multicast address; this lands on every copy, the
+//           sender's own included, so a copy shows the sum of both sides' signals
+// `base` is the value the flags hold when the call starts (counters are never reset).  The initiator
+// writes the mean round-trip time; a wait that runs out sets status = {2, round, wanted, seen}.
+__global__ void signal_pingpong_kernel(const int* local_flag, int* remote_flag, int mode, int initiator, int base, int rounds,
+                                       float* ns_per_rtt, int* status, unsigned long long timeout_ns) {
+  if (threadIdx.x != 0) return;
+  const unsigned long long t0 = globaltimer_ns();
+  const unsigned long long deadline = t0 + timeout_ns;
+  auto send = [&](int k) {
+    if (mode == 0) st_release_sys(remote_flag, base + k + 1);
+    else if (mode == 1) red_release_sys_add(remote_flag, 1);
+    else multimem_red_release_add(remote_flag, 1);
+  };
+  for (int k = 0; k < rounds; ++k) {
+    const int want = mode == 2 ? base + 2 * k + (initiator ? 2 : 1) : base + k + 1;
+    int seen = 0;
+    if (initiator) send(k);
+    if (!wait_ge<true>(local_flag, want, nullptr, deadline, &seen, 0)) {
+      if (atomicCAS(status, 0, 2) == 0) {
+        status[1] = k;
+        status[2] = want;
+        status[3] = seen;
+      }
+      return;
+    }
+    if (!initiator) send(k);
+  }
+  if (initiator) *ns_per_rtt = static_cast<float>(globaltimer_ns() - t0) / static_cast<float>(rounds);
+}
+
 int grid_for(size_t nvec, int blocks) {
   if (blocks > 0) return blocks;
   size_t b = (nvec + 1023) / 1024;
@@ -95,6 +129,13 @@ int tcl_barrier_all_mc(int32_t* mc_counter, const int32_t* local_counter, int wo
   if (!mc_counter || !local_counter || world < 1 || rank < 0 || rank >= world) return static_cast<int>(cudaErrorInvalidValue);
   barrier_all_mc_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(mc_counter, local_counter, world, rank, epoch, status,
                                                                       timeout_ns ? timeout_ns : 4000000000ull);
+  return static_cast<int>(cudaGetLastError());
+}
+int tcl_signal_pingpong(const int32_t* local_flag, int32_t* remote_flag, int mode, int initiator, int base, int rounds,
+                        float* ns_per_rtt, int32_t* status, uint64_t timeout_ns, void* stream) {
+  if (!local_flag || !remote_flag || mode < 0 || mode > 2 || rounds < 1) return static_cast<int>(cudaErrorInvalidValue);
+  signal_pingpong_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(local_flag, remote_flag, mode, initiator, base, rounds, ns_per_rtt,
+                                                                       status, timeout_ns ? timeout_ns : 2000000000ull);
   return static_cast<int>(cudaGetLastError());
 }
 }

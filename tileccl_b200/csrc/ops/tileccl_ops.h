@@ -89,6 +89,13 @@ int tcl_barrier_all(int32_t* const* counters, int world, int rank, int epoch, in
 int tcl_barrier_all_mc(int32_t* mc_counter, const int32_t* local_counter, int world, int rank, int epoch,
                        int32_t* status, uint64_t timeout_ns, void* stream);
 
+/* Flag ping-pong between two ranks, one launch on each: mode 0 st.release.sys, 1 red.release.sys.add,
+ * 2 multimem.red.release.add (remote_flag is then the multicast address; every copy counts both sides'
+ * signals).  `base` = value of the flags at the start.  The initiator writes the mean round trip in ns.
+ * The reference's ping-pong is tests/sync_cost.cu:82 (st.release only). */
+int tcl_signal_pingpong(const int32_t* local_flag, int32_t* remote_flag, int mode, int initiator, int base, int rounds,
+                        float* ns_per_rtt, int32_t* status, uint64_t timeout_ns, void* stream);
+
 /* out[r, c] = silu(gu[r, c]) * gu[r, ffn + c]; gu is [rows, 2*ffn] bf16. */
 int tcl_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t ffn, void* stream);
 
