@@ -155,6 +155,40 @@ __global__ void flat_copy_kernel(const uint4* __restrict__ src, uint4* __restric
   for (; i < nvec; i += st) ptx::st_v4(dst + i, ptx::ld_v4_stream(src + i));
 }
 
+// Load-only mover on the register path: a CTA brings tile after tile of the source into shared memory
+// with 16-byte ld.global (L1::no_allocate) + st.shared, four loads in flight per thread.  It is the
+// counterpart of kBulkLoadOnly without the bulk-copy engine: what a gather warp of a fused all-gather +
+// GEMM pays before the tile can reach the tensor core.  Dynamic shared memory: tile_vec * 16 bytes.
+__global__ void ldst_load_only_kernel(const uint4* __restrict__ src, size_t total_vec, uint32_t tile_vec, unsigned* sink) {
+  extern __shared__ __align__(16) uint4 ldst_tile[];
+  const size_t n_tiles = (total_vec + tile_vec - 1) / tile_vec;
+  unsigned acc = 0;
+  for (size_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const uint4* p = src + t * tile_vec;
+    const uint32_t len = static_cast<uint32_t>(total_vec - t * tile_vec < tile_vec ? total_vec - t * tile_vec : tile_vec);
+    uint32_t i = threadIdx.x;
+    for (; i + 3 * blockDim.x < len; i += 4 * blockDim.x) {
+      const uint4 a = ptx::ld_v4_stream(p + i), b = ptx::ld_v4_stream(p + i + blockDim.x);
+      const uint4 c = ptx::ld_v4_stream(p + i + 2 * blockDim.x), d = ptx::ld_v4_stream(p + i + 3 * blockDim.x);
+      ldst_tile[i] = a; ldst_tile[i + blockDim.x] = b; ldst_tile[i + 2 * blockDim.x] = c; ldst_tile[i + 3 * blockDim.x] = d;
+    }
+    for (; i < len; i += blockDim.x) ldst_tile[i] = ptx::ld_v4_stream(p + i);
+    __syncthreads();
+    acc += ldst_tile[(threadIdx.x * 7u) % len].x;  // the tile is consumed from shared memory
+    __syncthreads();
+  }
+  if (acc == 0xdeadbeefu) *sink = acc;
+}
+
+inline cudaError_t launch_ldst_load_only(int blocks, cudaStream_t st, const void* src, size_t total, uint32_t tile_bytes, unsigned* sink) {
+  const uint32_t tile_vec = tile_bytes / 16;
+  if (tile_vec == 0 || total % 16 != 0) return cudaErrorInvalidValue;
+  cudaError_t e = cudaFuncSetAttribute(ldst_load_only_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tile_vec * 16));
+  if (e != cudaSuccess) return e;
+  ldst_load_only_kernel<<<blocks, 256, tile_vec * 16, st>>>(static_cast<const uint4*>(src), total / 16, tile_vec, sink);
+  return cudaGetLastError();
+}
+
 inline size_t bulk_smem_bytes(int stages, uint32_t slot_stride) { return static_cast<size_t>(stages) * slot_stride + 8 * stages; }
 
 // Launch helper: picks the instantiation for `stages` in {3,4,6,8}.

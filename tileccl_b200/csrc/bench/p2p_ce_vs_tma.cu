@@ -1,11 +1,12 @@
-// p2p_ce_vs_tma: moving a [tokens x hidden] activation block to a peer, eight ways.
+// p2p_ce_vs_tma: moving a [tokens x hidden] activation block to a peer, nine ways.
 //   ce / ce_pull        copy engine, issued for the source / the destination device's stream
 //   sm / sm_pull        16-byte ld/st kernel running on the source (push) / destination (pull) GPU
 //   tma / tma_pull      bulk-copy ring through shared memory, push / pull
 //   tma_store           shared memory -> peer only (upper bound for a fused producer)
 //   tma_load            peer -> shared memory only (model of a fused consumer)
+//   sm_load             peer -> shared memory with 16-byte ld.global + st.shared (the same model on the register path)
 // Reports the average time of back-to-back transfers, the p50 / p99 of single transfers, GB/s, and a
-// host-side comparison of the destination (not for tma_store / tma_load, which move no complete copy).
+// host-side comparison of the destination (not for tma_store / tma_load / sm_load, which move no complete copy).
 //
 // Reference parity: tests/p2p_ce_vs_tma.cu (kernels :185-360, timing :483-550, tile plan :553-600,
 // table :873-879).  --csv is added here: method,tokens,hidden,bytes,avg_us,p50_us,p99_us,gbps,verify.
@@ -21,7 +22,7 @@ using namespace tcl::bench;
 int main(int argc, char** argv) {
   std::vector<int> tokens = {1, 4, 16, 64, 256, 1024, 4096};
   int hidden = 7168, elt = 2, tile_tokens = 0, stages = 4, blocks = 0, iters = 100, warmup = 20, src = 0, dst = 1;
-  std::vector<std::string> methods = {"ce", "ce_pull", "sm", "sm_pull", "tma", "tma_pull", "tma_store", "tma_load"};
+  std::vector<std::string> methods = {"ce", "ce_pull", "sm", "sm_pull", "tma", "tma_pull", "tma_store", "tma_load", "sm_load"};
   bool check = true;
   std::string csv_path, dtype = "bf16";
   Args a(argc, argv);
@@ -64,6 +65,8 @@ int main(int argc, char** argv) {
   TCL_CUDA_CHECK(cudaSetDevice(dst));
   TCL_CUDA_CHECK(cudaMalloc(&buf_d, max_bytes));
   TCL_CUDA_CHECK(cudaMalloc(&err_d, 4));
+  unsigned* sink_d = nullptr;
+  TCL_CUDA_CHECK(cudaMalloc(&sink_d, 4));
   TCL_CUDA_CHECK(cudaMemset(err_d, 0, 4));
   TCL_CUDA_CHECK(cudaSetDevice(src));
   TCL_CUDA_CHECK(cudaMalloc(&buf_s, max_bytes));
@@ -96,7 +99,7 @@ int main(int argc, char** argv) {
     if (tile > smem_budget) tile = smem_budget / 16 * 16;
     if (tile > bytes) tile = bytes;
     for (auto& m : methods) {
-      const bool pull = m == "ce_pull" || m == "sm_pull" || m == "tma_pull" || m == "tma_load";
+      const bool pull = m == "ce_pull" || m == "sm_pull" || m == "tma_pull" || m == "tma_load" || m == "sm_load";
       const int k = pull ? 1 : 0;  // which device runs the transfer
       int* err = pull ? err_d : err_s;
       TCL_CUDA_CHECK(cudaSetDevice(dst));
@@ -110,6 +113,8 @@ int main(int argc, char** argv) {
         } else if (m == "sm" || m == "sm_pull") {
           const int b = static_cast<int>(std::min<size_t>(4 * sms, (bytes / 16 + 255) / 256));
           flat_copy_kernel<<<std::max(1, b), 256, 0, st[k]>>>(reinterpret_cast<const uint4*>(buf_s), reinterpret_cast<uint4*>(buf_d), bytes / 16);
+        } else if (m == "sm_load") {
+          TCL_CUDA_CHECK(launch_ldst_load_only(nb, st[k], buf_s, bytes / 16 * 16, static_cast<uint32_t>(tile / 16 * 16), sink_d));
         } else {
           const int kind = m == "tma_store" ? kBulkStoreOnly : m == "tma_load" ? kBulkLoadOnly : kBulkCopy;
           TCL_CUDA_CHECK(launch_bulk_pipe(stages, nb, st[k], buf_s, buf_d, bytes, static_cast<uint32_t>(tile), kind, err, 2000000000ull));
@@ -135,7 +140,7 @@ int main(int argc, char** argv) {
       TCL_CUDA_CHECK(cudaMemcpy(&herr, err, 4, cudaMemcpyDeviceToHost));
       const char* ver = "-";
       if (herr) ver = "TIMEOUT";
-      else if (check && m != "tma_store" && m != "tma_load") {
+      else if (check && m != "tma_store" && m != "tma_load" && m != "sm_load") {
         TCL_CUDA_CHECK(cudaMemcpy(host_d.data(), buf_d, bytes, cudaMemcpyDeviceToHost));
         ver = std::memcmp(host_d.data(), host_s.data(), bytes) == 0 ? "ok" : "FAIL";
       }
