@@ -15,5 +15,5 @@ def _register():
 try:
     _t = _register()
     init, shutdown, symm_empty, heap, check_all = _t.init, _t.shutdown, _t.symm_empty, _t.heap, _t.check_all
-except Exception:  # torch missing or too old for torch.library: the C++ programs and the ctypes layer still work
+except (ImportError, AttributeError):  # torch missing or too old for torch.library: the C++ programs and the ctypes layer still work
     pass

@@ -43,7 +43,7 @@ class ClockSampler:
             self.proc.terminate()          # the exact process started above
             try:
                 self.proc.wait(timeout=5)
-            except Exception:
+            except subprocess.TimeoutExpired:
                 self.proc.kill()
             self.proc = None
 

@@ -27,8 +27,8 @@ def peaks() -> dict:
                 if k in d:
                     out[k] = float(d[k])
             out["source"] = "measured"
-        except Exception:
-            pass
+        except (OSError, ValueError, TypeError):   # unreadable or malformed file: keep the fallback figures
+            out = dict(FALLBACK, source="fallback")
     return out
 
 
