@@ -133,6 +133,7 @@ def lib() -> C.CDLL:
     sig("tcl_nvls_red", i32, [vp, vp, C.c_size_t, i32, vp])
     sig("tcl_p2p_copy", i32, [vp, vp, C.c_size_t, i32, vp])
     sig("tcl_barrier_all_mc", i32, [vp, vp, i32, i32, i32, vp, u64, vp])
+    sig("tcl_p2p_scatter", i32, [C.POINTER(vp), vp, C.c_size_t, i32, i32, i32, vp])
     sig("tcl_signal_pingpong", i32, [vp, vp, i32, i32, i32, i32, vp, vp, u64, vp])
     _lib = L
     return L

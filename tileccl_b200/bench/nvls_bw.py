@@ -2,6 +2,8 @@
 
     p2p_st      plain 16-byte stores into the next rank's heap (ring)
     p2p_ld      plain 16-byte loads from the next rank's heap
+    p2p_a2a     plain 16-byte stores of 1/world of the payload into EVERY peer's heap at once (the traffic pattern
+                of the fused GEMM + reduce-scatter epilogue; GB/s counts the (world-1)/world that leaves the GPU)
     mc_bcast    multimem.st: one store lands on every GPU (all-gather building block)
     mc_ldreduce multimem.ld_reduce: one load returns the sum over all GPUs, added inside the switch
     mc_red      multimem.red: one instruction adds into every GPU's copy
@@ -71,6 +73,7 @@ def main(argv=None) -> int:
     loc = torch.empty(mx, dtype=torch.uint8, device="cuda")
     loc.view(torch.bfloat16).fill_(1.0)
     bar = ew.DeviceBarrier(heap)
+    sym_ptrs = (C_.c_void_p * _native.MAX_WORLD)(*[heap.peer_ptr(sym, r) for r in range(world)])
     nxt = (rank + 1) % world
     st = lambda: C_.c_void_p(torch.cuda.current_stream().cuda_stream)  # noqa: E731
     vp = C_.c_void_p
@@ -78,7 +81,7 @@ def main(argv=None) -> int:
     if rank == 0:
         print(f"# nvls_bw world={world} multicast={'yes' if use_mc else 'no'} [{C.device_line()}]")
         print(f"{'mover':12s} {'bytes':>11s} | {'us':>10s} {'GB/s':>9s} | verify")
-    movers = ["p2p_st", "p2p_ld"] + (["mc_bcast", "mc_ldreduce", "mc_red"] if use_mc else []) + (["nccl_ag", "nccl_rs"] if world > 1 else [])
+    movers = ["p2p_st", "p2p_ld"] + (["p2p_a2a"] if world > 1 else []) + (["mc_bcast", "mc_ldreduce", "mc_red"] if use_mc else []) + (["nccl_ag", "nccl_rs"] if world > 1 else [])
     full = torch.empty(mx, dtype=torch.uint8, device="cuda")
     for n in sizes:
         for mv in movers:
@@ -91,6 +94,9 @@ def main(argv=None) -> int:
                     _native.check(lib.tcl_p2p_copy(vp(heap.peer_ptr(sym, nxt)), vp(loc.data_ptr()), n, args.blocks, st()), mv)
                 elif mv == "p2p_ld":
                     _native.check(lib.tcl_p2p_copy(vp(loc.data_ptr()), vp(heap.peer_ptr(sym, nxt)), n, args.blocks, st()), mv)
+                elif mv == "p2p_a2a":
+                    sl = n // world // 16 * 16
+                    _native.check(lib.tcl_p2p_scatter(sym_ptrs, vp(loc.data_ptr()), sl, world, rank, args.blocks, st()), mv)
                 elif mv == "mc_bcast":
                     # each rank broadcasts its 1/world slice: together an all-gather of n bytes
                     sl = n // world // 16 * 16
@@ -117,6 +123,18 @@ def main(argv=None) -> int:
                 got = loc[rank * sl: rank * sl + sl].view(torch.bfloat16)
                 verify = "ok" if bool((got == world * (world + 1) / 2).all()) else "FAIL"
                 loc.view(torch.bfloat16).fill_(1.0)
+            elif mv == "p2p_a2a":
+                loc.view(torch.bfloat16).fill_(float(rank + 1))
+                sym.zero_()
+                torch.cuda.synchronize(); G.host_barrier()
+                run()
+                torch.cuda.synchronize(); G.host_barrier()
+                sl = n // world // 16 * 16
+                got = sym[: sl * world].view(world, sl).view(torch.bfloat16)[:, 0::max(1, sl // 2 // 64)].float()
+                want = torch.arange(1, world + 1, device="cuda", dtype=torch.float32)[:, None].expand_as(got).clone()
+                want[rank] = 0.0   # the own slot is not written
+                verify = "ok" if bool((got == want).all()) and bool((sym[: sl * world].view(world, sl).view(torch.bfloat16)[:, -1].float() == want[:, 0]).all()) else "FAIL"
+                loc.view(torch.bfloat16).fill_(1.0)
             elif mv == "mc_bcast":
                 loc.view(torch.bfloat16).fill_(1.0)
                 sym.zero_()
@@ -127,7 +145,7 @@ def main(argv=None) -> int:
                 verify = "ok" if bool((sym[: sl * world].view(torch.bfloat16) == 1.0).all()) else "FAIL"
             us = C.stats_of(C.timed_series(run, args.iters, 3, before=bar)).p50
             us = G.max_over_ranks(us)
-            moved = (world - 1) / world * per * world if mv.startswith("nccl") else (n // world // 16 * 16 * (world - 1) if mv in ("mc_bcast", "mc_red") else
+            moved = (world - 1) / world * per * world if mv.startswith("nccl") else (n // world // 16 * 16 * (world - 1) if mv in ("mc_bcast", "mc_red", "p2p_a2a") else
                                                                                         (n // world // 16 * 16 if mv == "mc_ldreduce" else n))
             gbps = moved / us / 1e3
             bad = torch.tensor([1 if verify == "FAIL" else 0], device="cuda")

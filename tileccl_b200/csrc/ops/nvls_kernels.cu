@@ -47,6 +47,30 @@ __global__ void p2p_copy_kernel(uint4* dst, const uint4* __restrict__ src, size_
   for (; i < nvec; i += st) st_v4(dst + i, ld_v4_stream(src + i));
 }
 
+// All-to-all store: slice p of `src` (slice_vec vectors) goes to slot `rank` of peer p's buffer; block b
+// serves peer (b % peers), so every peer is written at the same time, as in the epilogue of the fused
+// GEMM + reduce-scatter.  The own slice is skipped.
+struct ScatterArgs {
+  uint4* dst[8];
+};
+__global__ void p2p_scatter_kernel(ScatterArgs a, const uint4* __restrict__ src, size_t slice_vec, int world, int rank) {
+  const int peers = world - 1;
+  const int which = blockIdx.x % peers;
+  const int peer = (rank + 1 + which) % world;
+  const size_t lane_blocks = gridDim.x / peers;          // blocks that serve this peer (the host makes it >= 1)
+  const size_t b = blockIdx.x / peers;
+  if (b >= lane_blocks) return;
+  const uint4* s = src + static_cast<size_t>(peer) * slice_vec;
+  uint4* d = a.dst[peer] + static_cast<size_t>(rank) * slice_vec;
+  const size_t st = lane_blocks * blockDim.x;
+  size_t i = b * blockDim.x + threadIdx.x;
+  for (; i + 3 * st < slice_vec; i += 4 * st) {
+    const uint4 v0 = ld_v4_stream(s + i), v1 = ld_v4_stream(s + i + st), v2 = ld_v4_stream(s + i + 2 * st), v3 = ld_v4_stream(s + i + 3 * st);
+    st_v4(d + i, v0); st_v4(d + i + st, v1); st_v4(d + i + 2 * st, v2); st_v4(d + i + 3 * st, v3);
+  }
+  for (; i < slice_vec; i += st) st_v4(d + i, ld_v4_stream(s + i));
+}
+
 // All-ranks barrier with ONE store per rank: the switch adds 1 to the counter's copy on every GPU.
 // The counter is an epoch counter (never reset): a rank leaves when its own copy reached epoch*world.
 // status = {code, rank, wanted, seen}; code 1 is the same "start barrier timed out" as the peer-store barrier.
@@ -136,6 +160,16 @@ int tcl_signal_pingpong(const int32_t* local_flag, int32_t* remote_flag, int mod
   if (!local_flag || !remote_flag || mode < 0 || mode > 2 || rounds < 1) return static_cast<int>(cudaErrorInvalidValue);
   signal_pingpong_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(local_flag, remote_flag, mode, initiator, base, rounds, ns_per_rtt,
                                                                        status, timeout_ns ? timeout_ns : 2000000000ull);
+  return static_cast<int>(cudaGetLastError());
+}
+int tcl_p2p_scatter(void* const* dst, const void* src, size_t slice_bytes, int world, int rank, int blocks, void* stream) {
+  if (world < 2 || world > 8 || rank < 0 || rank >= world || slice_bytes % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  ScatterArgs a = {};
+  for (int i = 0; i < world; ++i) a.dst[i] = static_cast<uint4*>(dst[i]);
+  const int peers = world - 1;
+  int per_peer = (blocks > 0 ? blocks : 148 * 4) / peers;
+  if (per_peer < 1) per_peer = 1;
+  p2p_scatter_kernel<<<per_peer * peers, 256, 0, static_cast<cudaStream_t>(stream)>>>(a, static_cast<const uint4*>(src), slice_bytes / 16, world, rank);
   return static_cast<int>(cudaGetLastError());
 }
 }

@@ -89,6 +89,10 @@ int tcl_barrier_all(int32_t* const* counters, int world, int rank, int epoch, in
 int tcl_barrier_all_mc(int32_t* mc_counter, const int32_t* local_counter, int world, int rank, int epoch,
                        int32_t* status, uint64_t timeout_ns, void* stream);
 
+/* All-to-all store: slice p of src goes to slot `rank` of dst[p] (every peer written at once; the own slice
+ * is skipped).  dst[] holds `world` device addresses, one per rank's buffer of world * slice_bytes. */
+int tcl_p2p_scatter(void* const* dst, const void* src, size_t slice_bytes, int world, int rank, int blocks, void* stream);
+
 /* Flag ping-pong between two ranks, one launch on each: mode 0 st.release.sys, 1 red.release.sys.add,
  * 2 multimem.red.release.add (remote_flag is then the multicast address; every copy counts both sides'
  * signals).  `base` = value of the flags at the start.  The initiator writes the mean round trip in ns.
