@@ -4,6 +4,8 @@ profiling with ncu (small case, few launches).
     python -m tileccl_b200.bench.once gemm --m 8192 --n 8192 --k 8192 --cta-group 2 --launches 3
     python -m tileccl_b200.bench.once gemm_rs --m 8192 --n 8192 --k 1024      (world of one, staged path)
     python -m tileccl_b200.bench.once silu_mul --m 16384 --n 3584
+    python -m tileccl_b200.bench.once ag_gemm --m 8192 --n 7168 --k 8192 --epi silu_mul   (world of one: flag-gated
+                                                    producer, gather warps idle, fused SiLU(gate)*up epilogue)
 
 The reference's counterpart is ``peer_l2_probe --modes once`` (l2_peer_cache/peer_l2_probe.cu:53-58).
 """
@@ -15,6 +17,7 @@ import sys
 import torch
 
 from ..ops import elementwise as ew
+from ..ops.ag_gemm import AgGemm
 from ..ops.gemm import GemmPlan
 from ..ops.gemm_rs import GemmRs
 from ..parallel.heap import SymmetricHeap
@@ -23,12 +26,13 @@ from . import _common as C
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "gemm_rs", "silu_mul"])
+    ap.add_argument("what", choices=["gemm", "gemm_rs", "silu_mul", "ag_gemm"])
     ap.add_argument("--m", type=C.parse_size, default=8192)
     ap.add_argument("--n", type=C.parse_size, default=8192)
     ap.add_argument("--k", type=C.parse_size, default=8192)
     ap.add_argument("--cta-group", type=int, default=2)
     ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--epi", default=None, choices=["silu_mul"], help="ag_gemm: fused activation epilogue")
     args = ap.parse_args(argv)
     dev = torch.device("cuda", torch.cuda.current_device())
     M, N, K = args.m, args.n, args.k
@@ -46,6 +50,11 @@ def main(argv=None) -> int:
         if args.what == "gemm":
             plan = GemmPlan(A, Bt, cta_group=args.cta_group)
             run, check = plan, plan.check
+        elif args.what == "ag_gemm":
+            heap = SymmetricHeap(M * K * 2 + (64 << 20))
+            op = AgGemm(heap, M, K, Bt, cta_group=args.cta_group, epi=args.epi)
+            op.a_shard.copy_(A)
+            run, check = op, op.check
         else:
             heap = SymmetricHeap(2 * M * N * 2 + (64 << 20))
             op = GemmRs(heap, A, Bt, cta_group=args.cta_group, force_staged=True)
