@@ -78,6 +78,40 @@ __global__ void reg_copy_kernel(const uint4* __restrict__ src, uint4* __restrict
   }
 }
 
+// Register mover with 256-bit loads and stores (ld/st.global.v8.b32, sm_100 and later): the same dealing of
+// messages as reg_copy_kernel, 32 bytes per thread per instruction.  `msg_vec8` counts 32-byte vectors;
+// the buffers must be 32-byte aligned.
+__global__ void reg256_copy_kernel(const ptx::Vec8* __restrict__ src, ptx::Vec8* __restrict__ dst, size_t n_msgs, size_t msg_vec8) {
+  const int lane = threadIdx.x & 31;
+  if (msg_vec8 <= 1024) {
+    const size_t warps_per_cta = blockDim.x >> 5;
+    const size_t gw = blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
+    const size_t n_gw = gridDim.x * warps_per_cta;
+    for (size_t m = gw; m < n_msgs; m += n_gw) {
+      const ptx::Vec8* s = src + m * msg_vec8;
+      ptx::Vec8* d = dst + m * msg_vec8;
+      size_t i = lane;
+      for (; i + 32 < msg_vec8; i += 64) {
+        const ptx::Vec8 a = ptx::ld_v8_stream(s + i), b = ptx::ld_v8_stream(s + i + 32);
+        ptx::st_v8(d + i, a); ptx::st_v8(d + i + 32, b);
+      }
+      for (; i < msg_vec8; i += 32) ptx::st_v8(d + i, ptx::ld_v8_stream(s + i));
+    }
+  } else {
+    for (size_t m = blockIdx.x; m < n_msgs; m += gridDim.x) {
+      const ptx::Vec8* s = src + m * msg_vec8;
+      ptx::Vec8* d = dst + m * msg_vec8;
+      size_t i = threadIdx.x;
+      const size_t st = blockDim.x;
+      for (; i + st < msg_vec8; i += 2 * st) {
+        const ptx::Vec8 a = ptx::ld_v8_stream(s + i), b = ptx::ld_v8_stream(s + i + st);
+        ptx::st_v8(d + i, a); ptx::st_v8(d + i + st, b);
+      }
+      for (; i < msg_vec8; i += st) ptx::st_v8(d + i, ptx::ld_v8_stream(s + i));
+    }
+  }
+}
+
 // What a bulk mover does with each tile.
 enum BulkKind : int { kBulkCopy = 0, kBulkLoadOnly = 1, kBulkStoreOnly = 2 };
 

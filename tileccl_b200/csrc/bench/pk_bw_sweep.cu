@@ -2,6 +2,7 @@
 //   ce   copy engine, one cudaMemcpyPeerAsync per message
 //   tma  bulk copies through shared memory (cp.async.bulk), multi-stage ring
 //   reg  16-byte ld/st through registers
+//   reg256  32-byte ld/st through registers (ld/st.global.v8.b32; not in the default list: --methods ce,tma,reg,reg256)
 // (a) against message size at full SM count, (b) against the number of SMs at
 // a fixed message size.  The destination is verified on the device.
 //
@@ -34,7 +35,7 @@ struct Config {
 
 static void usage(const char* p) {
   std::printf(
-      "usage: %s [--mode size|sms|both] [--total BYTES] [--sizes LIST] [--sms LIST] [--methods ce,tma,reg]\n"
+      "usage: %s [--mode size|sms|both] [--total BYTES] [--sizes LIST] [--sms LIST] [--methods ce,tma,reg,reg256]\n"
       "          [--blocks N] [--msg-tma BYTES] [--msg-reg BYTES] [--stages 3|4|6|8] [--reg-threads N]\n"
       "          [--iters N] [--warmup N] [--max-ce-msgs N] [--src N] [--dst N] [--no-check] [--csv FILE]\n"
       "  --src and --dst may be the same GPU (loop-back: measures the movers against local memory)\n", p);
@@ -83,6 +84,9 @@ static double run_point(Ctx& x, const std::string& method, size_t msg, size_t to
     } else if (method == "reg") {
       reg_copy_kernel<<<blocks, c.reg_threads, 0, x.st>>>(reinterpret_cast<const uint4*>(x.s), reinterpret_cast<uint4*>(x.d),
                                                             n_msgs, msg / 16);
+    } else if (method == "reg256") {
+      reg256_copy_kernel<<<blocks, c.reg_threads, 0, x.st>>>(reinterpret_cast<const tcl::ptx::Vec8*>(x.s), reinterpret_cast<tcl::ptx::Vec8*>(x.d),
+                                                               n_msgs, msg / 32);
     } else {
       // A message larger than a slot is moved as several tiles.
       const size_t budget = (x.smem_max - 8 * c.stages) / c.stages / 128 * 128;
@@ -167,6 +171,7 @@ int main(int argc, char** argv) {
       for (auto& m : c.methods) {
         bool ok = true;
         size_t total = c.total;
+        if (m == "reg256" && msg % 32) { std::printf(" %14s ", "-"); continue; }
         if (m == "ce" && total / msg > c.max_ce_msgs) total = c.max_ce_msgs * msg;
         const double us = run_point(x, m, msg, total, full_blocks, &ok);
         const double gbps = us > 0 ? (total / msg * msg) / us / 1e3 : 0.0;

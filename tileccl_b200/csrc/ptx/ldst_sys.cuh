@@ -126,6 +126,23 @@ __device__ __forceinline__ void st_v4(void* p, const uint4& v) {
                "r"(v.w)
                : "memory");
 }
+// 256-bit forms (sm_100 and later): one instruction moves 32 bytes; the address must be 32-byte aligned.
+struct alignas(32) Vec8 {
+  uint32_t w[8];
+};
+__device__ __forceinline__ Vec8 ld_v8_stream(const void* p) {
+  Vec8 v;
+  asm volatile("ld.global.L1::no_allocate.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7])
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_v8(void* p, const Vec8& v) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]),
+               "r"(v.w[3]), "r"(v.w[4]), "r"(v.w[5]), "r"(v.w[6]), "r"(v.w[7])
+               : "memory");
+}
 __device__ __forceinline__ void st_v4_stream(void* p, const uint4& v) {
   asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x),
                "r"(v.y), "r"(v.z), "r"(v.w)
