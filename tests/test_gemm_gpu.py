@@ -75,6 +75,28 @@ def test_gemm_rs_world1_reduces_its_own_partials(native_lib, cta_group):
     heap.close()
 
 
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_gemm_rs_world1_32_byte_stores(native_lib, cta_group):
+    """The opt-in epilogue with st.global.v8.b32 gives the same bits as the 16-byte one."""
+    from tileccl_b200.ops.gemm_rs import GemmRs
+    from tileccl_b200.parallel.heap import SymmetricHeap
+    torch.manual_seed(11)
+    M, N, K = 512, 768, 192
+    heap = SymmetricHeap(64 << 20)
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    ref_op = GemmRs(heap, A, Bt, cta_group=cta_group, force_staged=True, timeout_ms=1000)
+    op = GemmRs(heap, A, Bt, cta_group=cta_group, force_staged=True, timeout_ms=1000, st256=True)
+    op.stage.fill_(float("nan"))
+    want = ref_op().clone()
+    ref_op.check()
+    got = op()
+    op.check()
+    assert torch.equal(got, want)
+    assert _rel(got, _ref(A, Bt)) < 1e-2
+    heap.close()
+
+
 def test_ag_gemm_world1(native_lib):
     from tileccl_b200.ops.ag_gemm import AgGemm
     from tileccl_b200.parallel.heap import SymmetricHeap

@@ -63,6 +63,7 @@ class GemmDesc(C.Structure):
         ("range_hi", C.c_uint64 * MAX_WORLD),
         ("epi_silu_mul", C.c_int32),
         ("ablate", C.c_int32),
+        ("epi_st256", C.c_int32),
     ]
 
 

@@ -50,6 +50,7 @@ def build_parser():
     ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--ablate", type=int, default=0, help="timing-only knobs of the fused variant: 1 = no reduce warps, 2 = no tile signals, 3 = both")
     ap.add_argument("--transport", default="p2p", choices=["p2p", "nvls"], help="p2p: epilogue pushes partial tiles to the owner; nvls: partials stay local, the owner pulls sums with multimem.ld_reduce")
+    ap.add_argument("--st256", action="store_true", help="fused variant: 32-byte epilogue stores (st.global.v8.b32) instead of 16-byte ones")
     ap.add_argument("--verify", action="store_true")
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between iterations")
     ap.add_argument("--csv", default=None)
@@ -72,7 +73,7 @@ def main(argv=None) -> int:
     D = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     plain = GemmPlan(A, Bt, out=D, cta_group=args.cta_group)
     fused = GemmRs(heap, A, Bt, cta_group=args.cta_group, rs_chunks=args.rs_chunks, group_m=args.group_m,
-                   ablate=args.ablate, transport=args.transport)
+                   ablate=args.ablate, transport=args.transport, st256=args.st256)
     ctrl = GemmRs(heap, A, Bt, cta_group=args.cta_group, rs_chunks=args.rs_chunks, group_m=args.group_m,
                   comm_enabled=False)
     bar = ew.DeviceBarrier(heap)

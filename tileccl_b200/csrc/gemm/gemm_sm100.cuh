@@ -85,6 +85,7 @@ struct GemmParams {
   int epoch;      // 1-based call number of the plan that owns the flag buffers
   int comm_enabled;
   int epi_silu_mul;  // epilogue computes silu(gate) * up from the two 128-column halves of every tile; D is [M, N/2]
+  int epi_st256;  // the plain epilogue stores 32 bytes per lane (st.global.v8.b32); needs 32-byte aligned destinations and pitch
   int ablate;     // experiment knobs (timing only): bit 0 = no reduce warps, bit 1 = no tile signals,
                   // bit 2 = AG+GEMM producer does not wait for gathered rows
 
@@ -562,6 +563,32 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (half == 0) continue;
         __syncwarp();
+        if (p.epi_st256) {
+          // 8 lanes cover one row's 256 contiguous bytes with 32-byte stores; 4 rows per store instruction.
+          // A lane reads its two 16-byte slots in an order that keeps each quarter-warp on 8 different banks.
+          const int ch8 = lane & 7;
+          const int swap = ch8 >> 2;
+          const int ccol8 = (c - 1) * Cfg::EPI_CHUNK_COLS + ch8 * 16;   // column inside the tile
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3);
+            const uint4 wa = lds_v4(my_buf + r * 256 + (((2 * ch8 + swap) ^ (r & 7)) << 4));
+            const uint4 wb = lds_v4(my_buf + r * 256 + (((2 * ch8 + 1 - swap) ^ (r & 7)) << 4));
+            const uint4 lo = swap ? wb : wa, hi = swap ? wa : wb;
+            const int grow = row0 + q * 32 + r;
+            if (grow < p.M && col0 + ccol8 < p.N) {
+              __nv_bfloat16* a = dst0 + static_cast<long long>(q * 32 + r) * p.ldc + ccol8;
+              if (p.mode != kModeGemmRs || detail::in_range(p, s_abort, seg, a, 32)) {
+                Vec8 v;
+                v.w[0] = lo.x; v.w[1] = lo.y; v.w[2] = lo.z; v.w[3] = lo.w;
+                v.w[4] = hi.x; v.w[5] = hi.y; v.w[6] = hi.z; v.w[7] = hi.w;
+                st_v8(a, v);
+              }
+            }
+          }
+          __syncwarp();
+          continue;
+        }
         // 16 lanes cover one row's 256 contiguous bytes; 2 rows per store instruction.
         const int ch = lane & 15;
         const int ccol = (c - 1) * Cfg::EPI_CHUNK_COLS + ch * 8;   // column inside the tile

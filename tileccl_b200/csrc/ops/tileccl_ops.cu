@@ -241,6 +241,12 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
   p.comm_enabled = d->comm_enabled;
   p.ablate = d->ablate;
   p.epi_silu_mul = d->epi_silu_mul;
+  p.epi_st256 = d->epi_st256;
+  if (d->epi_st256) {
+    bool aligned = d->ldc % 16 == 0 && !d->epi_silu_mul;
+    for (int s = 0; s < nseg; ++s) aligned = aligned && (reinterpret_cast<uintptr_t>(d->dst_base[s]) & 31) == 0;
+    if (!aligned) { set_err(err, errlen, "epi_st256 needs 32-byte aligned dst_base, ldc a multiple of 16 and no epi_silu_mul"); delete pl; return nullptr; }
+  }
   if (d->epi_silu_mul && d->mode == TCL_MODE_GEMM_RS) { set_err(err, errlen, "epi_silu_mul is not available for GEMM+RS"); delete pl; return nullptr; }
   p.seg_rows = d->seg_rows;
   for (int s = 0; s < TCL_MAX_WORLD; ++s) {

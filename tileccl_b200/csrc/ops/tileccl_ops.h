@@ -61,6 +61,8 @@ typedef struct tcl_gemm_desc {
   int32_t epi_silu_mul; /* plain / AG+GEMM: every 256-column tile holds 128 gate columns then the 128 up columns of the same
                            features; the epilogue writes silu(gate) * up: D is [M, N/2] (ldc is its pitch) */
   int32_t ablate;       /* experiments only: bit 0 = no reduce warps, bit 1 = no tile signals */
+  int32_t epi_st256;    /* the epilogue stores 32 bytes per lane (st.global.v8.b32) instead of 16; every dst_base must be
+                           32-byte aligned and ldc a multiple of 16 elements; not with epi_silu_mul */
 } tcl_gemm_desc;
 
 /* Returns NULL and fills err on invalid arguments. */
