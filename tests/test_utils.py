@@ -29,7 +29,7 @@ def test_csv_headers_match_reference_layout():
     assert csvio.EXP3_FUSED_COLUMNS[:27] == ("m,n,k,world,rank,base_us,base_p95,ctrl_us,ctrl_p95,fused_us,fused_p95,struct_sd,comm_sd,total_sd,"
                                              "pull_gbps,max_rel_diff,base_p50,ctrl_p50,fused_p50,base_min,ctrl_min,fused_min,comm_sd_p50,"
                                              "comm_sd_skew,comm_abs_us,order,iters").split(",")
-    assert csvio.EXP3_FUSED_COLUMNS[27:] == csvio.EXTRA_COLUMNS
+    assert csvio.EXP3_FUSED_COLUMNS[27:] == csvio.EXTRA_COLUMNS + ["knobs"]   # appended only, after the reference's 27
     assert csvio.SIGNAL_FANIN_COLUMNS == "mode,fanin,bytes,min_us,p50_us,p95_us,p99_us,verify".split(",")
     assert csvio.EXP2_COLUMNS[:4] == ["m", "n", "k", "world"] and "seg_eff" in csvio.EXP2_COLUMNS
 

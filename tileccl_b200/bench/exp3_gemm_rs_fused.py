@@ -48,6 +48,7 @@ def build_parser():
     ap.add_argument("--cta-group", type=int, default=2)
     ap.add_argument("--rs-chunks", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
+    ap.add_argument("--num-ctas", type=int, default=0, help="CTAs of the fused and ctrl variants (0 = one per SM)")
     ap.add_argument("--ablate", type=int, default=0, help="timing-only knobs of the fused variant: 1 = no reduce warps, 2 = no tile signals, 3 = both")
     ap.add_argument("--transport", default="p2p", choices=["p2p", "nvls"], help="p2p: epilogue pushes partial tiles to the owner; nvls: partials stay local, the owner pulls sums with multimem.ld_reduce")
     ap.add_argument("--st256", action="store_true", help="fused variant: 32-byte epilogue stores (st.global.v8.b32) instead of 16-byte ones")
@@ -72,9 +73,9 @@ def main(argv=None) -> int:
     ew.fill_normal_(Bt, seed=2000 + rank)
     D = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     plain = GemmPlan(A, Bt, out=D, cta_group=args.cta_group)
-    fused = GemmRs(heap, A, Bt, cta_group=args.cta_group, rs_chunks=args.rs_chunks, group_m=args.group_m,
+    fused = GemmRs(heap, A, Bt, cta_group=args.cta_group, rs_chunks=args.rs_chunks, group_m=args.group_m, num_ctas=args.num_ctas,
                    ablate=args.ablate, transport=args.transport, st256=args.st256)
-    ctrl = GemmRs(heap, A, Bt, cta_group=args.cta_group, rs_chunks=args.rs_chunks, group_m=args.group_m,
+    ctrl = GemmRs(heap, A, Bt, cta_group=args.cta_group, rs_chunks=args.rs_chunks, group_m=args.group_m, num_ctas=args.num_ctas,
                   comm_enabled=False)
     bar = ew.DeviceBarrier(heap)
     out_nccl = torch.empty(M // world, N, dtype=torch.bfloat16, device=dev) if world > 1 else None
@@ -148,7 +149,9 @@ def main(argv=None) -> int:
                     comm_sd_skew=(f.mean / ctrl_max if ctrl_max > 0 else 0.0), comm_abs_us=f.mean - c.mean,
                     order="|".join(order), iters=args.iters, max_over_ranks_us=fused_max, nccl_cublas_us=nccl_max,
                     speedup=(nccl_max / fused_max if fused_max > 0 else 0.0), roofline_us=roof["roofline_us"],
-                    pct_roofline=(100.0 * roof["roofline_us"] / fused_max if fused_max > 0 else 0.0), dtype="bf16")
+                    pct_roofline=(100.0 * roof["roofline_us"] / fused_max if fused_max > 0 else 0.0), dtype="bf16",
+                    knobs=f"cta_group={args.cta_group}|transport={fused.transport}|rs_chunks={args.rs_chunks}|group_m={args.group_m}|"
+                          f"num_ctas={args.num_ctas}|st256={int(args.st256)}|ablate={args.ablate}")
         csv.close()
         if fused_max > 0:
             print(f"max over ranks: fused {fused_max:.1f} us | nccl+cublas {nccl_max:.1f} us | speedup "

@@ -15,7 +15,7 @@ EXTRA_COLUMNS = ["max_over_ranks_us", "nccl_cublas_us", "speedup", "roofline_us"
 # comm_comp/exp3_gemm_rs_fused.cu:575-580
 EXP3_FUSED_COLUMNS = ("m,n,k,world,rank,base_us,base_p95,ctrl_us,ctrl_p95,fused_us,fused_p95,struct_sd,comm_sd,"
                       "total_sd,pull_gbps,max_rel_diff,base_p50,ctrl_p50,fused_p50,base_min,ctrl_min,fused_min,"
-                      "comm_sd_p50,comm_sd_skew,comm_abs_us,order,iters").split(",") + EXTRA_COLUMNS
+                      "comm_sd_p50,comm_sd_skew,comm_abs_us,order,iters").split(",") + EXTRA_COLUMNS + ["knobs"]
 # comm_comp/exp3_gemm_rs_fused.cu:501 (per-iteration dump, one file per rank)
 EXP3_ITER_COLUMNS = "m,n,k,world,rank,variant,iter,us".split(",")
 # comm_comp/exp2_ag_gemm_granularity.cu:446-448
