@@ -1,5 +1,4 @@
 """Verdict reducers of the analysis script, on synthetic bundles."""
-import os
 
 from tileccl_b200.bench import analyze, run_all
 from tileccl_b200.utils import csvio

@@ -5,7 +5,6 @@ import ctypes as C
 from hypothesis import given, settings
 from hypothesis import strategies as st
 
-from tileccl_b200 import _native
 from tileccl_b200.parallel import tiling
 
 

@@ -1,5 +1,4 @@
 """Host-side helpers: size/shape parsing, statistics, CSV layout, roofline arithmetic, clocks."""
-import os
 
 import pytest
 

@@ -6,7 +6,6 @@ import os
 
 import torch
 
-from ..ops import elementwise as ew
 from ..parallel import group as G
 from ..utils.stats import make_stats
 

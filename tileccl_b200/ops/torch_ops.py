@@ -19,7 +19,6 @@ from __future__ import annotations
 
 import torch
 
-from ..parallel import group as G
 from ..parallel.heap import SymmetricHeap
 from . import elementwise as ew
 from .ag_gemm import AgGemm
