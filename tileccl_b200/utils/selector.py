@@ -1,0 +1,131 @@
+"""Transport selector: the decision table of the probe suite as code.
+
+The reference ends its analysis with a decision table (which transport for which situation) and a
+vector of platform parameters that an automatic chooser would need, and lists "encode the table
+as a back-end selector plus one parameter file per platform" as its next milestone
+(tests/ANALYSIS.md:118-173).  This module is that selector for B200 / NVLink 5 / NVSwitch.
+
+The parameters are the figures this suite measured on 8 x B200 (``reports/REPORT_b200.md`` gives the
+runs): ``pk_bw_sweep`` (link bandwidth per mover, SMs to saturate, per-copy cost of the copy engine),
+``p2p_ce_vs_tma`` (one-shot latencies), ``sync_cost`` (one-way latency, cost of a release flag),
+``interference_matrix`` / ``exp1_ce_interference`` (what a transfer costs a concurrent kernel).
+Another platform overrides them with ``Platform.from_json``.
+
+The model is the zero-parameter one the reference validates with ``pipeline_e2e``:
+a pipelined producer -> transfer -> consumer takes ``max(Tc_src, Tm, Tc_dst)``; a transfer takes
+``start + n_msgs * per_message + bytes / bandwidth``; a transport that occupies SMs slows an SM-bound
+kernel by the share of SMs it takes, one that does not by its measured interference factor.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+
+TRANSPORTS = ("ce", "reg", "bulk", "fused_st", "fused_pull")
+
+
+@dataclass
+class Platform:
+    name: str = "B200 NVLink5 NVSwitch"
+    sms: int = 148
+    # link bandwidth per direction, GB/s
+    ce_gbps: float = 749.0            # copy engine, 128 MB copy
+    sm_gbps: float = 700.0            # register or bulk-copy mover, any message >= 2 KB
+    per_sm_gbps: float = 50.0         # what one SM of a mover sustains; 16 SMs saturate the link
+    fused_st_gbps: float = 620.0      # 16-byte peer stores from a GEMM epilogue (all-to-all pattern)
+    fused_pull_gbps: float = 705.0    # peer loads by gather warps of all SMs
+    # fixed costs, microseconds
+    ce_per_copy_us: float = 3.7       # each cudaMemcpyPeerAsync beyond its bytes
+    launch_us: float = 4.0            # a mover kernel of its own
+    one_way_us: float = 2.6           # store becomes visible at the peer
+    flag_us: float = 1.45             # release flag after a payload (st.release, fence + st, red.release alike)
+    min_msg_reg: int = 512            # below this a message no longer reaches sm_gbps
+    min_msg_bulk: int = 2048
+    # slow-down of a concurrent kernel (S_c) when the transfer does not take its SMs, by what bounds the kernel
+    # (interference_matrix, probe on 132 SMs and mover on 16; "tensor" for ce is exp1's GEMM under 7 pull legs)
+    s_c: dict = field(default_factory=lambda: {
+        "ce": {"tensor": 1.03, "hbm": 1.01, "l2": 1.14},
+        "reg": {"tensor": 1.01, "hbm": 1.06, "l2": 1.25},
+        "bulk": {"tensor": 1.00, "hbm": 1.03, "l2": 1.97},
+        "fused_st": {"tensor": 1.00, "hbm": 1.06, "l2": 1.25},
+        "fused_pull": {"tensor": 1.00, "hbm": 1.06, "l2": 1.25},
+    })
+    # slow-down of the transfer itself (S_m) under that kernel
+    s_m: dict = field(default_factory=lambda: {
+        "ce": {"tensor": 1.00, "hbm": 1.08, "l2": 1.01},
+        "reg": {"tensor": 1.02, "hbm": 1.09, "l2": 1.01},
+        "bulk": {"tensor": 1.02, "hbm": 1.19, "l2": 1.02},
+        "fused_st": {"tensor": 1.00, "hbm": 1.09, "l2": 1.01},
+        "fused_pull": {"tensor": 1.00, "hbm": 1.09, "l2": 1.01},
+    })
+
+    @classmethod
+    def from_json(cls, path: str) -> "Platform":
+        with open(path) as f:
+            d = json.load(f)
+        base = asdict(cls())
+        unknown = set(d) - set(base)
+        if unknown:
+            raise ValueError(f"unknown platform parameters: {sorted(unknown)}")
+        base.update(d)
+        return cls(**base)
+
+    def to_json(self, path: str) -> None:
+        with open(path, "w") as f:
+            json.dump(asdict(self), f, indent=1)
+
+
+def transfer_us(p: Platform, transport: str, nbytes: int, n_msgs: int = 1, sms: int = 16) -> float:
+    """Time of one transfer of ``nbytes`` split in ``n_msgs`` equal messages."""
+    if transport not in TRANSPORTS:
+        raise ValueError(f"unknown transport {transport!r}")
+    if nbytes <= 0:
+        return 0.0
+    n_msgs = max(1, n_msgs)
+    msg = nbytes / n_msgs
+    if transport == "ce":
+        return n_msgs * p.ce_per_copy_us + nbytes / (p.ce_gbps * 1e3) + p.one_way_us
+    if transport in ("reg", "bulk"):
+        bw = min(p.sm_gbps, p.per_sm_gbps * max(1, sms))
+        floor = p.min_msg_reg if transport == "reg" else p.min_msg_bulk
+        if msg < floor:                      # short messages: the per-message issue cost shows
+            bw *= msg / floor
+        return p.launch_us + nbytes / (bw * 1e3) + p.one_way_us
+    bw = p.fused_st_gbps if transport == "fused_st" else p.fused_pull_gbps
+    return nbytes / (bw * 1e3) + p.one_way_us + p.flag_us      # no launch: it rides in the compute kernel
+
+
+def compute_slowdown(p: Platform, transport: str, bound: str = "tensor", sms: int = 16) -> float:
+    """Factor by which a kernel bound by ``bound`` (tensor, hbm, l2) slows while the transfer runs."""
+    if bound not in ("tensor", "hbm", "l2"):
+        raise ValueError("bound must be tensor, hbm or l2")
+    f = p.s_c[transport][bound]
+    if transport in ("reg", "bulk") and bound == "tensor":
+        f *= p.sms / max(1, p.sms - sms)     # a mover kernel of its own takes whole SMs from an SM-bound kernel
+    return f
+
+
+def pipeline_us(tc_src: float, tm: float, tc_dst: float) -> float:
+    """Steady-state time of a tile pipeline producer -> transfer -> consumer."""
+    return max(tc_src, tm, tc_dst)
+
+
+def choose(p: Platform, nbytes: int, n_msgs: int = 1, compute_us: float = 0.0, bound: str = "tensor",
+           fused_possible: bool = False, sms_spare: int = 16) -> dict:
+    """Ranks the transports for moving ``nbytes`` while a kernel of ``compute_us`` runs.
+
+    Returns ``{"best": name, "table": {name: {"comm_us", "compute_us", "total_us"}}}`` where total is the
+    overlapped time ``max(comm, slowed compute)``.  ``fused_possible`` says the data is produced or consumed
+    by a kernel that can carry the transfer itself (epilogue stores, gather warps).
+    """
+    table = {}
+    for t in TRANSPORTS:
+        if t.startswith("fused") and not fused_possible:
+            continue
+        if t in ("reg", "bulk") and sms_spare <= 0:
+            continue
+        comm = transfer_us(p, t, nbytes, n_msgs, sms_spare) * (p.s_m[t][bound] if compute_us > 0 else 1.0)
+        comp = compute_us * compute_slowdown(p, t, bound, sms_spare) if compute_us > 0 else 0.0
+        table[t] = {"comm_us": comm, "compute_us": comp, "total_us": max(comm, comp)}
+    best = min(table, key=lambda k: (table[k]["total_us"], table[k]["comm_us"]))
+    return {"best": best, "table": table}
