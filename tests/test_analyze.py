@@ -75,3 +75,17 @@ def test_manifest_resume_and_plan(tmp_path):
         assert want in names
     assert len(set(names)) == len(names)
     assert "2 not ok" in analyze.report(str(tmp_path))
+
+
+def test_tuning_summary_sorts_knob_settings(tmp_path):
+    w = csvio.CsvAppender(str(tmp_path / "exp3_tuning.csv"), csvio.EXP3_FUSED_COLUMNS)
+    dflt = "cta_group=2|transport=p2p|rs_chunks=0|group_m=0|num_ctas=0|st256=0|ablate=0"
+    fast = "cta_group=2|transport=p2p|rs_chunks=0|group_m=0|num_ctas=0|st256=1|ablate=0"
+    for rank in (0, 1):
+        _fused_row(w, rank=rank, max_over_ranks_us=800.0, nccl_cublas_us=1200.0, knobs=dflt)
+        _fused_row(w, rank=rank, max_over_ranks_us=700.0, nccl_cublas_us=1190.0, knobs=fast)
+    w.close()
+    txt = analyze.report(str(tmp_path))
+    lines = [line for line in txt.splitlines() if "st256=" in line]
+    assert len(lines) == 2 and "st256=1" in lines[0] and "700.0" in lines[0] and "1.143x of default" in lines[0]
+    assert "1.000x of default" in lines[1] and "1.500x of NCCL+cuBLAS" in lines[1]

@@ -227,12 +227,31 @@ def interference_sanity(bundle: str) -> str:
     return "\n".join(out) + "\n"
 
 
+def tuning_summary(rows: list[dict]) -> str:
+    """Knob sweep of the fused GEMM+RS (``run_all --tuning``): one line per knob setting, fastest first."""
+    if not rows:
+        return ""
+    best: dict[str, tuple[float, float]] = {}
+    for r in rows:
+        t, n = _f(r, "max_over_ranks_us"), _f(r, "nccl_cublas_us")
+        if t > 0:
+            best[r.get("knobs", "?")] = (t, n)       # every rank's row carries the same max over ranks
+    if not best:
+        return ""
+    out = ["## knob sweep of the fused GEMM+RS (max over ranks)"]
+    ref = best.get(next((k for k in best if "rs_chunks=0|group_m=0|num_ctas=0|st256=0" in k and "cta_group=2" in k and "transport=p2p" in k), ""), None)
+    for k, (t, n) in sorted(best.items(), key=lambda kv: kv[1][0]):
+        rel = f"  {ref[0] / t:5.3f}x of default" if ref else ""
+        out.append(f"  {t:9.1f} us  {n / t if t else 0:5.3f}x of NCCL+cuBLAS{rel}  {k}")
+    return "\n".join(out) + "\n"
+
+
 def report(bundle: str) -> str:
     parts = [f"# analysis of {bundle}\n"]
     ms = read(os.path.join(bundle, "exp3_fused_msweep.csv"))
     ks = read(os.path.join(bundle, "exp3_fused_ksweep.csv"))
     parts += [msweep(ms), verdict_shift_or_tail(ms), verdict_tiles_or_duration(ks), verdict_order(read(os.path.join(bundle, "exp3_order.csv"))),
-              verdict_tail_shape(bundle), exp2_summary(read(os.path.join(bundle, "exp2.csv"))), l2_verdict(bundle), interference_sanity(bundle)]
+              verdict_tail_shape(bundle), tuning_summary(read(os.path.join(bundle, "exp3_tuning.csv"))), exp2_summary(read(os.path.join(bundle, "exp2.csv"))), l2_verdict(bundle), interference_sanity(bundle)]
     mf = os.path.join(bundle, "manifest.txt")
     if os.path.exists(mf):
         lines = open(mf).read().splitlines()
