@@ -65,6 +65,16 @@ def main(argv=None) -> int:
     M, N = args.m, args.n
     K = args.k if args.k > 0 else args.k_global // world
     dev = torch.device("cuda", torch.cuda.current_device())
+    # A rank's segment must hold whole tiles: 256 rows for CTA pairs, 128 for single CTAs.
+    if M % world == 0 and (M // world) % (128 * args.cta_group) and (M // world) % 128 == 0:
+        if rank == 0:
+            print(f"# M / world = {M // world} rows is not a multiple of {128 * args.cta_group}: using --cta-group 1")
+        args.cta_group = 1
+    if M % world or (M // world) % 128 or N % 256 or K % 8:
+        if rank == 0:
+            print(f"# skipped: M={M} N={N} K/rank={K} world={world} does not tile (M/world % 128, N % 256, K % 8)")
+        G.shutdown()
+        return 0
     nvls = args.transport == "nvls" and world > 1
     heap = SymmetricHeap(2 * (M * N * 2 + (M // world) * N * 2) + (64 << 20), backend="vmm" if nvls else "ipc", multicast=nvls)
     A = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
