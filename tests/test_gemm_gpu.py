@@ -1,4 +1,6 @@
 """tcgen05 GEMM kernels vs a plain PyTorch fp32 reference (single GPU)."""
+import os
+
 import pytest
 import torch
 
@@ -95,6 +97,42 @@ def test_gemm_rs_world1_32_byte_stores(native_lib, cta_group):
     assert torch.equal(got, want)
     assert _rel(got, _ref(A, Bt)) < 1e-2
     heap.close()
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_plain_gemm_32_byte_stores(native_lib, cta_group):
+    from tileccl_b200.ops.gemm import GemmPlan
+    torch.manual_seed(12)
+    A = torch.randn(512, 320, device="cuda", dtype=torch.bfloat16)
+    Bt = torch.randn(768, 320, device="cuda", dtype=torch.bfloat16)
+    want = GemmPlan(A, Bt, cta_group=cta_group, timeout_ms=1000)().clone()
+    plan = GemmPlan(A, Bt, cta_group=cta_group, timeout_ms=1000, store="st256")
+    got = plan()
+    plan.check()
+    assert torch.equal(got, want)
+
+
+@pytest.mark.skipif(os.environ.get("TILECCL_TEST_TMA_EPILOGUE") != "1",
+                    reason="the TMA-store epilogue has not run on a GPU yet: first run it alone with TILECCL_TEST_TMA_EPILOGUE=1")
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_plain_gemm_tma_store_epilogue(native_lib, cta_group):
+    """cp.async.bulk.tensor stores from the staging buffer give the same bits as st.global, also with row
+    segments routed to separate buffers."""
+    from tileccl_b200.ops.gemm import GemmPlan
+    torch.manual_seed(13)
+    M, N, K = 1024, 768, 320
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    want = GemmPlan(A, Bt, cta_group=cta_group, timeout_ms=1000)().clone()
+    plan = GemmPlan(A, Bt, cta_group=cta_group, timeout_ms=1000, store="tma")
+    got = plan()
+    plan.check()
+    assert torch.equal(got, want)
+    parts = [torch.full((M // 2, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    seg = GemmPlan(A, Bt, cta_group=cta_group, timeout_ms=1000, store="tma", seg_rows=M // 2, dst_ptrs=[t.data_ptr() for t in parts])
+    seg()
+    seg.check()
+    assert torch.equal(torch.cat(parts, 0), want)
 
 
 def test_ag_gemm_world1(native_lib):

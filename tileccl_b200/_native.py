@@ -64,6 +64,7 @@ class GemmDesc(C.Structure):
         ("epi_silu_mul", C.c_int32),
         ("ablate", C.c_int32),
         ("epi_st256", C.c_int32),
+        ("epi_tma_store", C.c_int32),
     ]
 
 

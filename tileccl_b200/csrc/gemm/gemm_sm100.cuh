@@ -85,6 +85,8 @@ struct GemmParams {
   int epoch;      // 1-based call number of the plan that owns the flag buffers
   int comm_enabled;
   int epi_silu_mul;  // epilogue computes silu(gate) * up from the two 128-column halves of every tile; D is [M, N/2]
+  int epi_tma_store;  // the plain epilogue leaves through TMA: cp.async.bulk.tensor stores of 32 x 64 boxes from the
+                      // warp's staging buffer (not with GEMM+RS communication, not with epi_silu_mul)
   int epi_st256;  // the plain epilogue stores 32 bytes per lane (st.global.v8.b32); needs 32-byte aligned destinations and pitch
   int ablate;     // experiment knobs (timing only): bit 0 = no reduce warps, bit 1 = no tile signals,
                   // bit 2 = AG+GEMM producer does not wait for gathered rows
@@ -128,6 +130,12 @@ struct GemmParams {
 
   int* status;                   // [4]: code, blockIdx, detail0, detail1
   unsigned long long timeout_ns;
+};
+
+// Tensor maps of the output, one per row segment (box 32 rows x 64 columns, 128-byte swizzle); only read
+// when GemmParams::epi_tma_store is set.
+struct OutMaps {
+  CUtensorMap m[kMaxWorld];
 };
 
 template <int kCtaGroup>
@@ -253,7 +261,8 @@ template <int kCtaGroup>
 __global__ void __launch_bounds__(GemmCfg<kCtaGroup>::THREADS, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ GemmParams p) {
+                  const __grid_constant__ GemmParams p,
+                  const __grid_constant__ OutMaps omaps) {
   using Cfg = GemmCfg<kCtaGroup>;
   using namespace ptx;
 
@@ -543,6 +552,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // 64-column TMEM reads.  Row `lane`, 16-byte slot k is stored at slot k ^ (lane & 7):
         // the row-wise writes and the transposed reads are both bank-conflict free.
         const int half = c & 1;
+        if (p.epi_tma_store && half == 0) {
+          // the stores of the previous pair of chunks must have read the buffer before it is rewritten
+          if (lane == 0) bulk_wait_read<0>();
+          __syncwarp();
+        }
+        // Row `lane`, 64-column half `half`: eight 16-byte slots, slot k at k ^ (lane & 7).  For the TMA
+        // epilogue the two halves are two 32 x 128-byte tiles in the 128-byte-swizzle layout of the tensor
+        // map; otherwise they sit side by side in 256-byte rows (the same bytes, another pitch).
+        const uint32_t wr = p.epi_tma_store ? my_buf + half * 4096 + lane * 128 : my_buf + lane * 256 + half * 128;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 w;
@@ -550,7 +568,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           w.y = pack_bf16x2(v0[8 * j + 2], v0[8 * j + 3]);
           w.z = pack_bf16x2(v0[8 * j + 4], v0[8 * j + 5]);
           w.w = pack_bf16x2(v0[8 * j + 6], v0[8 * j + 7]);
-          sts_v4(my_buf + lane * 256 + (((half * 8 + j) ^ (lane & 7)) << 4), w);
+          sts_v4(wr + ((j ^ (lane & 7)) << 4), w);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -559,9 +577,22 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           w.y = pack_bf16x2(v1[8 * j + 2], v1[8 * j + 3]);
           w.z = pack_bf16x2(v1[8 * j + 4], v1[8 * j + 5]);
           w.w = pack_bf16x2(v1[8 * j + 6], v1[8 * j + 7]);
-          sts_v4(my_buf + lane * 256 + (((half * 8 + j + 4) ^ (lane & 7)) << 4), w);
+          sts_v4(wr + (((j + 4) ^ (lane & 7)) << 4), w);
         }
         if (half == 0) continue;
+        if (p.epi_tma_store) {
+          // every lane orders its shared-memory writes before the asynchronous proxy reads them
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            const int x = col0 + (c - 1) * Cfg::EPI_CHUNK_COLS;                      // a multiple of 64 elements
+            const int y = row0 - seg * p.seg_rows + q * 32;                          // row inside the segment's tensor
+            tma_store_2d(&omaps.m[seg], my_buf, x, y);
+            tma_store_2d(&omaps.m[seg], my_buf + 4096, x + Cfg::EPI_CHUNK_COLS, y);
+            bulk_commit();
+          }
+          continue;
+        }
         __syncwarp();
         if (p.epi_st256) {
           // 8 lanes cover one row's 256 contiguous bytes with 32-byte stores; 4 rows per store instruction.
@@ -617,6 +648,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+    // TMA epilogue: the stores must have left shared memory and reached global memory before the CTA ends
+    if (p.epi_tma_store && lane == 0) bulk_wait<0>();
   } else if (warp < Cfg::SIGNAL_WARP) {
     // ===== communication warps =====
     const int cw = warp - (2 + Cfg::EPI_WARPS);

@@ -17,6 +17,7 @@ struct GemmPlan {
   CUtensorMap tmap_a;
   CUtensorMap tmap_b;
   GemmParams params;
+  OutMaps omaps;     // encoded only for the TMA-store epilogue
   int cta_group;
   int grid;
 };
@@ -51,7 +52,7 @@ cudaError_t launch_gemm(const GemmPlan* pl, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<G>, pl->tmap_a, pl->tmap_b, pl->params);
+  return cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<G>, pl->tmap_a, pl->tmap_b, pl->params, pl->omaps);
 }
 
 // ---------------------------------------------------------------------------
@@ -242,6 +243,23 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
   p.ablate = d->ablate;
   p.epi_silu_mul = d->epi_silu_mul;
   p.epi_st256 = d->epi_st256;
+  p.epi_tma_store = d->epi_tma_store;
+  if (d->epi_tma_store) {
+    if (d->epi_silu_mul || d->epi_st256 || (d->mode == TCL_MODE_GEMM_RS && d->comm_enabled)) {
+      set_err(err, errlen, "epi_tma_store excludes epi_silu_mul, epi_st256 and the communicating GEMM+RS");
+      delete pl;
+      return nullptr;
+    }
+    for (int s = 0; s < nseg; ++s) {
+      const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(d->dst_base[s]) + d->dst_row_off[s] * static_cast<long long>(d->ldc);
+      if (ptx::encode_tmap_bf16_k64(&pl->omaps.m[s], base, static_cast<uint64_t>(d->seg_rows), static_cast<uint64_t>(d->N),
+                                    static_cast<uint64_t>(d->ldc), 32) != 0) {
+        set_err(err, errlen, "cuTensorMapEncodeTiled failed for an output segment");
+        delete pl;
+        return nullptr;
+      }
+    }
+  }
   if (d->epi_st256) {
     bool aligned = d->ldc % 16 == 0 && !d->epi_silu_mul;
     for (int s = 0; s < nseg; ++s) aligned = aligned && (reinterpret_cast<uintptr_t>(d->dst_base[s]) & 31) == 0;

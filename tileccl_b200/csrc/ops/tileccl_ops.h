@@ -63,6 +63,8 @@ typedef struct tcl_gemm_desc {
   int32_t ablate;       /* experiments only: bit 0 = no reduce warps, bit 1 = no tile signals */
   int32_t epi_st256;    /* the epilogue stores 32 bytes per lane (st.global.v8.b32) instead of 16; every dst_base must be
                            32-byte aligned and ldc a multiple of 16 elements; not with epi_silu_mul */
+  int32_t epi_tma_store; /* the epilogue leaves through TMA (cp.async.bulk.tensor stores from the staging buffer) instead of
+                            st.global; plain and AG+GEMM modes and the non-communicating GEMM+RS; not with epi_silu_mul */
 } tcl_gemm_desc;
 
 /* Returns NULL and fills err on invalid arguments. */

@@ -41,6 +41,16 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtens
       : "memory");
 }
 
+// 2-D tiled store this CTA's shared memory -> global, joined to the calling thread's bulk group.
+// The box that leaves shared memory is the tensor map's box; rows and columns beyond the tensor's
+// extent are clipped by the hardware.  x must be a multiple of 8 bf16 elements; x and y not negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src_smem, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src_smem), "r"(x), "r"(y)
+               : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

@@ -15,9 +15,15 @@ from ._plan import Plan, require_bf16_rowmajor
 class GemmPlan(Plan):
     def __init__(self, A: torch.Tensor, Bt: torch.Tensor, out: torch.Tensor | None = None,
                  cta_group: int = 2, group_m: int = 0, num_ctas: int = 0, timeout_ms: float = 4000.0,
-                 dst_ptrs: list[int] | None = None, seg_rows: int | None = None, epi: str | None = None):
+                 dst_ptrs: list[int] | None = None, seg_rows: int | None = None, epi: str | None = None,
+                 store: str = "st16"):
         """``dst_ptrs``/``seg_rows`` route row segments of D to other addresses
-        (a peer's buffer): the epilogue-remote experiment."""
+        (a peer's buffer): the epilogue-remote experiment.  ``store`` picks how the epilogue leaves the
+        SM: ``st16`` (16-byte st.global, the default), ``st256`` (32-byte st.global.v8.b32) or ``tma``
+        (cp.async.bulk.tensor stores from the staging buffer), the counterparts of the reference's
+        direct-store and TMA-store epilogues (comm_comp/gemm_sm90.cuh:83-88)."""
+        if store not in ("st16", "st256", "tma"):
+            raise ValueError("store must be st16, st256 or tma")
         require_bf16_rowmajor(A, "A")
         require_bf16_rowmajor(Bt, "Bt")
         M, K = A.shape
@@ -47,6 +53,8 @@ class GemmPlan(Plan):
         d.timeout_ns = int(timeout_ms * 1e6)
         d.group_m, d.num_ctas = group_m, num_ctas
         d.epi_silu_mul = 1 if epi == "silu_mul" else 0
+        d.epi_st256 = 1 if store == "st256" else 0
+        d.epi_tma_store = 1 if store == "tma" else 0
         super().__init__(d, keep_alive=(A, Bt, out))
         self.out = out
 
