@@ -25,3 +25,18 @@ def test_instruction_descriptor_fields(native_lib):
         assert (i >> 17) & 0x3F == n >> 3
         assert (i >> 24) & 0x1F == m >> 4
         assert i & 0xF == 0 and (i >> 13) & 0x3 == 0    # dense, no negation
+
+
+def test_binding_restates_the_c_struct(native_lib):
+    """Size and field offsets of the ctypes GemmDesc equal those of tcl_gemm_desc in the built library."""
+    import ctypes as C
+
+    from tileccl_b200 import _native
+    assert native_lib.tcl_gemm_desc_size() == C.sizeof(_native.GemmDesc)
+    checked = 0
+    for name, _ in _native.GemmDesc._fields_:
+        off = native_lib.tcl_gemm_desc_offset(name.encode())
+        if off >= 0:
+            assert off == getattr(_native.GemmDesc, name).offset, name
+            checked += 1
+    assert checked >= 20 and native_lib.tcl_gemm_desc_offset(b"no_such_field") == -1

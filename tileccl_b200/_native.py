@@ -75,6 +75,17 @@ def available() -> bool:
     return _LIB_PATH.exists()
 
 
+def check_desc_layout(L) -> None:
+    """The ctypes restatement of ``tcl_gemm_desc`` must have the size and the field offsets of the C
+    struct the library was built with; a stale library or an edited binding fails here, not in a kernel."""
+    if L.tcl_gemm_desc_size() != C.sizeof(GemmDesc):
+        raise RuntimeError(f"tcl_gemm_desc is {L.tcl_gemm_desc_size()} bytes in the library and {C.sizeof(GemmDesc)} in the binding: rebuild")
+    for name, _ in GemmDesc._fields_:
+        off = L.tcl_gemm_desc_offset(name.encode())
+        if off >= 0 and off != getattr(GemmDesc, name).offset:
+            raise RuntimeError(f"tcl_gemm_desc.{name}: offset {off} in the library, {getattr(GemmDesc, name).offset} in the binding")
+
+
 def lib() -> C.CDLL:
     """The loaded library; raises with a build hint when it is missing."""
     global _lib
@@ -93,6 +104,9 @@ def lib() -> C.CDLL:
         f.restype = res
         f.argtypes = args
 
+    sig("tcl_gemm_desc_size", i32, [])
+    sig("tcl_gemm_desc_offset", i32, [C.c_char_p])
+    check_desc_layout(L)
     sig("tcl_gemm_plan_create", vp, [C.POINTER(GemmDesc), C.c_char_p, i32])
     sig("tcl_gemm_plan_run", i32, [vp, i32, vp])
     sig("tcl_gemm_plan_destroy", None, [vp])

@@ -4,6 +4,7 @@
 #include "tileccl_ops.h"
 
 #include <cstdio>
+#include <cstddef>
 #include <cstring>
 #include <new>
 
@@ -188,6 +189,19 @@ __global__ void max_rel_err_final(const float* scratch, int nblocks, float* resu
 }  // namespace
 
 extern "C" {
+
+int tcl_gemm_desc_size(void) { return static_cast<int>(sizeof(tcl_gemm_desc)); }
+
+int tcl_gemm_desc_offset(const char* field) {
+  if (!field) return -1;
+#define TCL_OFF(name) if (std::strcmp(field, #name) == 0) return static_cast<int>(offsetof(tcl_gemm_desc, name));
+  TCL_OFF(mode) TCL_OFF(M) TCL_OFF(lda) TCL_OFF(A) TCL_OFF(world) TCL_OFF(seg_rows) TCL_OFF(dst_base) TCL_OFF(dst_row_off)
+  TCL_OFF(rs_tile_cnt) TCL_OFF(rs_stage) TCL_OFF(rs_chunks) TCL_OFF(ag_src) TCL_OFF(ag_flags) TCL_OFF(gather_rows) TCL_OFF(ag_done)
+  TCL_OFF(ag_push) TCL_OFF(ag_dst) TCL_OFF(barrier) TCL_OFF(status) TCL_OFF(timeout_ns) TCL_OFF(group_m) TCL_OFF(rs_mc_stage)
+  TCL_OFF(range_lo) TCL_OFF(epi_silu_mul) TCL_OFF(ablate) TCL_OFF(epi_st256) TCL_OFF(epi_tma_store)
+#undef TCL_OFF
+  return -1;
+}
 
 int tcl_gemm_smem_bytes(int cta_group) {
   return cta_group == 2 ? GemmCfg<2>::SMEM_BYTES : GemmCfg<1>::SMEM_BYTES;

@@ -67,6 +67,11 @@ typedef struct tcl_gemm_desc {
                             st.global; plain and AG+GEMM modes and the non-communicating GEMM+RS; not with epi_silu_mul */
 } tcl_gemm_desc;
 
+/* Layout check for bindings that restate the struct: its size, and the offset of the named field
+ * (-1 for an unknown name). */
+int tcl_gemm_desc_size(void);
+int tcl_gemm_desc_offset(const char* field);
+
 /* Returns NULL and fills err on invalid arguments. */
 void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen);
 /* Launches one call; epoch is the 1-based call number shared by all ranks. */
