@@ -59,8 +59,8 @@ def test_plan_rejects_bad_shapes(native_lib):
 
 @pytest.mark.parametrize("cta_group", [1, 2])
 def test_gemm_rs_world1_reduces_its_own_partials(native_lib, cta_group):
-    """World of one: the epilogue stages locally, the reduce warps wait on the
-    tile counters and produce the output - the whole fused path minus NVLink."""
+    """World of one: nothing to reduce, the epilogue writes the shard itself (the staged path with the
+    signalling and reduce warps is forced in test_gemm_rs_world1_32_byte_stores)."""
     from tileccl_b200.ops.gemm_rs import GemmRs
     from tileccl_b200.parallel.heap import SymmetricHeap
     torch.manual_seed(5)
@@ -229,3 +229,28 @@ def test_fused_silu_mul_epilogue(native_lib, cta_group):
     assert out.shape == (M, F)
     ref = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
     assert _rel(out, ref) < 1e-2
+
+
+def test_torch_op_layer_single_gpu(native_lib):
+    """torch.ops.tileccl.* on one GPU (world of one): plans are cached per operand set."""
+    import tileccl_b200 as tc
+    torch.manual_seed(21)
+    A = torch.randn(512, 384, device="cuda", dtype=torch.bfloat16)
+    Bt = torch.randn(768, 384, device="cuda", dtype=torch.bfloat16)
+    ref = _ref(A, Bt)
+    tc.init(128 << 20)
+    try:
+        assert _rel(torch.ops.tileccl.gemm(A, Bt), ref) < 1e-2
+        assert _rel(torch.ops.tileccl.gemm_rs(A, Bt), ref) < 1e-2
+        y1 = torch.ops.tileccl.ag_gemm(A, Bt)
+        assert _rel(y1, ref) < 1e-2
+        A2 = torch.randn_like(A)
+        y2 = torch.ops.tileccl.ag_gemm(A2, Bt)            # same plan, new shard contents
+        assert y2.data_ptr() == y1.data_ptr() and _rel(y2, _ref(A2, Bt)) < 1e-2
+        gu = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16)
+        g, u = gu[:, :256].float(), gu[:, 256:].float()
+        assert _rel(torch.ops.tileccl.silu_mul(gu), torch.nn.functional.silu(g) * u) < 2e-2
+        torch.ops.tileccl.barrier()
+        tc.check_all()
+    finally:
+        tc.shutdown()
