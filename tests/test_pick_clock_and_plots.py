@@ -71,8 +71,21 @@ def test_figures_from_csv(tmp_path):
         for comm in ("ce", "reg"):
             w.row(mode="matrix", probe=probe, comm=comm, probe_dev="src", S_m=1.1, S_c=1.02)
     w.close()
+    w = csvio.CsvAppender(str(tmp_path / "nvls_bw.csv"), "mover,bytes,world,us,gbps,verify".split(","))
+    for mover in ("p2p_st", "mc_bcast"):
+        for b in (65536, 1 << 24):
+            w.row(mover=mover, bytes=b, world=8, us=10.0, gbps=b / 1e5, verify="-")
+    w.row(mover="barrier_mc", bytes=0, world=8, us=14.0, gbps=0.0, verify="-")      # latency rows stay out of the figure
+    w.close()
+    w = csvio.CsvAppender(str(tmp_path / "exp3_tuning.csv"), csvio.EXP3_FUSED_COLUMNS)
+    for knobs, us in (("cta_group=2|transport=p2p|rs_chunks=0|group_m=0|num_ctas=0|st256=0|ablate=0", 800.0),
+                      ("cta_group=2|transport=p2p|rs_chunks=0|group_m=0|num_ctas=0|st256=1|ablate=0", 700.0)):
+        w.row(m=32768, n=8192, k=1024, world=8, rank=0, max_over_ranks_us=us, nccl_cublas_us=1200.0, roofline_us=610.0, knobs=knobs)
+    w.close()
     made = plots.make_all(str(tmp_path))
     names = {os.path.basename(p) for p in made}
-    assert {"pk_bw_vs_size.svg", "pk_bw_vs_sms.svg", "interference_S_c.svg", "interference_S_m.svg"} <= names
+    assert {"pk_bw_vs_size.svg", "pk_bw_vs_sms.svg", "interference_S_c.svg", "interference_S_m.svg", "nvls_bw.svg", "gemm_rs_tuning.svg"} <= names
+    tune = open(os.path.join(str(tmp_path), "figs", "gemm_rs_tuning.svg")).read()
+    assert "st256=1" in tune and "default" in tune and "barrier_mc" not in open(os.path.join(str(tmp_path), "figs", "nvls_bw.svg")).read()
     svg = open(made[0]).read()
     assert svg.startswith("<svg") and "polyline" in svg and "reg" in svg

@@ -192,6 +192,27 @@ def make_all(bundle: str) -> list[str]:
             p = os.path.join(figs, f"interference_{metric}.svg")
             bar_chart(p, probes, ser, f"interference matrix: {metric}", metric, ref_line=1.0)
             done(p)
+    r = [x for x in _rows(bundle, "nvls_bw.csv") if _num(x, "bytes") > 0]
+    if r:
+        s = {}
+        for row in r:
+            s.setdefault(row["mover"], []).append((_num(row, "bytes"), _num(row, "gbps")))
+        p = os.path.join(figs, "nvls_bw.svg")
+        line_chart(p, s, "NVSwitch paths: bandwidth per rank vs payload (all ranks active)", "payload (bytes)", "GB/s", logx=True, logy=True)
+        done(p)
+    r = _rows(bundle, "exp3_tuning.csv")
+    if r:
+        best: dict = {}
+        for row in r:
+            if _num(row, "max_over_ranks_us") > 0:
+                best[row.get("knobs", "?")] = (_num(row, "max_over_ranks_us"), _num(row, "nccl_cublas_us"), _num(row, "roofline_us"))
+        if best:
+            ks = sorted(best, key=lambda k: best[k][0])
+            short = ["|".join(kv for kv in k.split("|") if not kv.endswith("=0") and kv not in ("transport=p2p", "cta_group=2")) or "default" for k in ks]
+            p = os.path.join(figs, "gemm_rs_tuning.svg")
+            bar_chart(p, short, {"fused": [best[k][0] for k in ks], "NCCL+cuBLAS": [best[k][1] for k in ks], "roofline": [best[k][2] for k in ks]},
+                      "GEMM+RS knob sweep (max over ranks)", "us")
+            done(p)
     r = _rows(bundle, "pipeline_e2e.csv")
     if r:
         s = {}
