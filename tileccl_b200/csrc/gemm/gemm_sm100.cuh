@@ -83,6 +83,9 @@ struct GemmParams {
   TileSched sched;
   int world, rank;
   int epoch;      // 1-based call number of the plan that owns the flag buffers
+  int* epoch_dev; // optional, two ints in device memory: [0] calls of this plan that have completed, [1] CTAs of
+                  // the running call that have finished.  When set, the call number is [0] + 1 instead of `epoch`
+                  // and the last CTA to finish advances it: the launch can then be replayed from a CUDA graph.
   int comm_enabled;
   int epi_silu_mul;  // epilogue computes silu(gate) * up from the two 128-column halves of every tile; D is [M, N/2]
   int epi_tma_store;  // the plain epilogue leaves through TMA: cp.async.bulk.tensor stores of 32 x 64 boxes from the
@@ -292,6 +295,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int group_id = blockIdx.x / kCtaGroup;
   const int num_groups = gridDim.x / kCtaGroup;
   const unsigned long long deadline = globaltimer_ns() + p.timeout_ns;
+  // Call number: from the host, or from the plan's device word (stable during the call: it is advanced by the
+  // last CTA to finish, after every CTA has read it here).
+  const int epoch = p.epoch_dev ? ld_relaxed_sys(p.epoch_dev) + 1 : p.epoch;
 
   const TileSched sched = p.sched;
   const int num_tiles = sched.num_tiles();
@@ -333,7 +339,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   tc_fence_after_sync();
   const uint32_t tmem_base = *s_tmem_ptr;
-  const int barrier_target = detail::epoch_times(p.epoch, p.world);
+  const int barrier_target = detail::epoch_times(epoch, p.world);
 
   // ---- roles ----------------------------------------------------------------
   if (warp == 0) {
@@ -349,7 +355,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (p.mode == kModeAgGemm && fused_comm && !(p.ablate & 4) && (m0 / p.seg_rows) != p.rank) {
           // Rows [m0, m0+BM) lie in one gather block (gather_rows % BM == 0).
           const int blk = m0 / p.gather_rows;
-          const int target = detail::epoch_times(p.epoch, p.gather_rows / p.ag_item_rows);
+          const int target = detail::epoch_times(epoch, p.gather_rows / p.ag_item_rows);
           int seen = 0;
           const bool landed = p.ag_push ? wait_ge<true>(p.ag_flags + blk, target, s_abort, deadline, &seen)
                                         : wait_ge<false>(p.ag_flags + blk, target, s_abort, deadline, &seen);
@@ -658,7 +664,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // ---- reduce warps: sum the `world` staged partials of each tile of this
       // rank's segment, in the order in which the producers complete them ----
       const int items = (p.seg_rows / Cfg::BM) * sched.n_tiles;
-      const int target = detail::epoch_times(p.epoch, p.world);
+      const int target = detail::epoch_times(epoch, p.world);
       const size_t slot_elems = static_cast<size_t>(p.seg_rows) * p.N;
       for (int j = blockIdx.x; j < items; j += gridDim.x) {
         if (ctid == 0) {
@@ -795,7 +801,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // the last gather warp of the grid sends one signal per peer.
         if (lane == 0) {
           const int done = atom_add_acq_rel_gpu(p.ag_done, 1) + 1;
-          if (done == detail::epoch_times(p.epoch, n_gw)) {
+          if (done == detail::epoch_times(epoch, n_gw)) {
             for (int s = 0; s < p.world; ++s)
               if (s != p.rank) red_release_sys_add(p.ag_read_done[s], 1);
           }
@@ -804,8 +810,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // this rank's shard, so the caller may overwrite it after the kernel.
         if (blockIdx.x == 0 && cw == 0 && lane == 0) {
           int seen = 0;
-          if (!wait_ge<true>(p.ag_read_done[p.rank], detail::epoch_times(p.epoch, p.world - 1), s_abort, deadline, &seen, 512)) {
-            detail::report(p, s_abort, kErrAgEndBarrier, detail::epoch_times(p.epoch, p.world - 1), seen);
+          if (!wait_ge<true>(p.ag_read_done[p.rank], detail::epoch_times(epoch, p.world - 1), s_abort, deadline, &seen, 512)) {
+            detail::report(p, s_abort, kErrAgEndBarrier, detail::epoch_times(epoch, p.world - 1), seen);
           }
         }
       }
@@ -854,6 +860,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc<kCtaGroup>(tmem_base, Cfg::TMEM_COLS);
+  }
+  if (p.epoch_dev != nullptr && threadIdx.x == 0) {
+    // Count this CTA out; the last one resets the count and advances the plan's call number.
+    __threadfence();
+    if (atomicAdd(p.epoch_dev + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      p.epoch_dev[1] = 0;
+      __threadfence();
+      atomicAdd(p.epoch_dev, 1);
+    }
   }
 }
 

@@ -198,7 +198,7 @@ int tcl_gemm_desc_offset(const char* field) {
   TCL_OFF(mode) TCL_OFF(M) TCL_OFF(lda) TCL_OFF(A) TCL_OFF(world) TCL_OFF(seg_rows) TCL_OFF(dst_base) TCL_OFF(dst_row_off)
   TCL_OFF(rs_tile_cnt) TCL_OFF(rs_stage) TCL_OFF(rs_chunks) TCL_OFF(ag_src) TCL_OFF(ag_flags) TCL_OFF(gather_rows) TCL_OFF(ag_done)
   TCL_OFF(ag_push) TCL_OFF(ag_dst) TCL_OFF(barrier) TCL_OFF(status) TCL_OFF(timeout_ns) TCL_OFF(group_m) TCL_OFF(rs_mc_stage)
-  TCL_OFF(range_lo) TCL_OFF(epi_silu_mul) TCL_OFF(ablate) TCL_OFF(epi_st256) TCL_OFF(epi_tma_store)
+  TCL_OFF(range_lo) TCL_OFF(epi_silu_mul) TCL_OFF(ablate) TCL_OFF(epi_st256) TCL_OFF(epi_tma_store) TCL_OFF(epoch_dev)
 #undef TCL_OFF
   return -1;
 }
@@ -257,6 +257,7 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
   p.ablate = d->ablate;
   p.epi_silu_mul = d->epi_silu_mul;
   p.epi_st256 = d->epi_st256;
+  p.epoch_dev = d->epoch_dev;
   p.epi_tma_store = d->epi_tma_store;
   if (d->epi_tma_store) {
     if (d->epi_silu_mul || d->epi_st256 || (d->mode == TCL_MODE_GEMM_RS && d->comm_enabled)) {

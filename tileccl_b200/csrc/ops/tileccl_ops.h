@@ -65,6 +65,9 @@ typedef struct tcl_gemm_desc {
                            32-byte aligned and ldc a multiple of 16 elements; not with epi_silu_mul */
   int32_t epi_tma_store; /* the epilogue leaves through TMA (cp.async.bulk.tensor stores from the staging buffer) instead of
                             st.global; plain and AG+GEMM modes and the non-communicating GEMM+RS; not with epi_silu_mul */
+  int32_t* epoch_dev;    /* optional: two zeroed ints in device memory.  When set, the kernel takes the call number from
+                            epoch_dev[0] + 1 (and advances it when the call ends) instead of the `epoch` argument of
+                            tcl_gemm_plan_run, so that a captured CUDA graph can replay the launch */
 } tcl_gemm_desc;
 
 /* Layout check for bindings that restate the struct: its size, and the offset of the named field

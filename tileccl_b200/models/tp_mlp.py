@@ -34,7 +34,7 @@ def heap_bytes(tokens: int, hidden: int, ffn: int, world: int) -> int:
 class TpMlp:
     def __init__(self, heap: SymmetricHeap, tokens: int, hidden: int = 8192, ffn: int = 28672,
                  cta_group: int = 2, gather_rows: int = 512, seed: int = 0, init_std: float = 0.02,
-                 fuse_silu: bool = True):
+                 fuse_silu: bool = True, graph: bool = False):
         world, rank = heap.world, heap.rank
         if ffn % world or tokens % world:
             raise ValueError("ffn and tokens must be divisible by the world size")
@@ -53,12 +53,14 @@ class TpMlp:
         if self.fuse_silu:
             self.h = None
             self.ag = AgGemm(heap, tokens, hidden, self.w_gate_up, cta_group=cta_group,
-                             gather_rows=gather_rows, out=self.act, epi="silu_mul")
+                             gather_rows=gather_rows, out=self.act, epi="silu_mul", device_epoch=graph)
         else:
             self.h = torch.empty(tokens, 2 * f, dtype=torch.bfloat16, device=dev)
             self.ag = AgGemm(heap, tokens, hidden, self.w_gate_up, cta_group=cta_group,
-                             gather_rows=gather_rows, out=self.h)
-        self.rs = GemmRs(heap, self.act, self.w_down, cta_group=cta_group)
+                             gather_rows=gather_rows, out=self.h, device_epoch=graph)
+        self.rs = GemmRs(heap, self.act, self.w_down, cta_group=cta_group, device_epoch=graph)
+        self._graph = None
+        self._want_graph = graph
 
     @property
     def x_shard(self) -> torch.Tensor:
@@ -72,6 +74,23 @@ class TpMlp:
         return self.rs(stream)
 
     __call__ = forward
+
+    def capture(self, warmup: int = 2):
+        """Captures the block (two or three launches) in a CUDA graph; needs ``graph=True`` at construction
+        so that the kernels keep their call numbers in device memory.  ``replay()`` then runs the block with
+        one launch from the host and returns the output buffer.  Collective: every rank captures and replays
+        in step."""
+        if not self._want_graph:
+            raise RuntimeError("build the block with graph=True to capture it")
+        from ..ops._plan import capture_graph
+        self._graph = capture_graph(self.forward, warmup)
+        return self._graph
+
+    def replay(self) -> torch.Tensor:
+        if self._graph is None:
+            raise RuntimeError("capture() first")
+        self._graph.replay()
+        return self.rs.out
 
     def check(self) -> None:
         self.ag.check()

@@ -28,7 +28,8 @@ from ._plan import Plan, require_bf16_rowmajor
 class AgGemm:
     def __init__(self, heap: SymmetricHeap, M: int, K: int, Bt: torch.Tensor, cta_group: int = 2,
                  gather_rows: int = 512, out: torch.Tensor | None = None, group_m: int = 0,
-                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "pull", item_rows: int = 1, epi: str | None = None):
+                 num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "pull", item_rows: int = 1, epi: str | None = None,
+                 device_epoch: bool = False):
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
         world, rank = heap.world, heap.rank
@@ -87,7 +88,7 @@ class AgGemm:
         d.timeout_ns = int(timeout_ms * 1e6)
         d.group_m, d.num_ctas = group_m, num_ctas
         d.ablate = ablate
-        self.plan = Plan(d, keep_alive=(Bt, out, self.a_full, self.flags, self.done, self.barrier))
+        self.plan = Plan(d, keep_alive=(Bt, out, self.a_full, self.flags, self.done, self.barrier), device_epoch=device_epoch)
         self.gather_rows = gather_rows
 
     def __call__(self, stream=None) -> torch.Tensor:

@@ -28,7 +28,7 @@ class GemmRs:
     def __init__(self, heap: SymmetricHeap, A: torch.Tensor, Bt: torch.Tensor, cta_group: int = 2,
                  rs_chunks: int = 0, comm_enabled: bool = True, group_m: int = 0, num_ctas: int = 0,
                  timeout_ms: float = 4000.0, ablate: int = 0, force_staged: bool = False, transport: str = "p2p",
-                 st256: bool = False):
+                 st256: bool = False, device_epoch: bool = False):
         require_bf16_rowmajor(A, "A")
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
@@ -96,7 +96,7 @@ class GemmRs:
         d.group_m, d.num_ctas = group_m, num_ctas
         d.ablate = ablate
         d.epi_st256 = 1 if st256 else 0    # 32-byte epilogue stores (st.global.v8.b32) instead of 16-byte ones
-        self.plan = Plan(d, keep_alive=(A, Bt, self.stage, self.tile_cnt, self.barrier, self.out))
+        self.plan = Plan(d, keep_alive=(A, Bt, self.stage, self.tile_cnt, self.barrier, self.out), device_epoch=device_epoch)
         self.rs_chunks = rs_chunks
 
     def __call__(self, stream=None) -> torch.Tensor:
