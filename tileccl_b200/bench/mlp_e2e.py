@@ -32,6 +32,7 @@ def main(argv=None) -> int:
     ap.add_argument("--cta-group", type=int, default=2)
     ap.add_argument("--gather-rows", type=int, default=512)
     ap.add_argument("--no-fuse-silu", action="store_true", help="keep SiLU*mul as its own kernel")
+    ap.add_argument("--graph", action="store_true", help="also time the block replayed from a CUDA graph (call numbers kept in device memory)")
     ap.add_argument("--verify", action="store_true")
     ap.add_argument("--csv", default=None)
     args = ap.parse_args(argv)
@@ -40,7 +41,7 @@ def main(argv=None) -> int:
     f = F // world
     dev = torch.device("cuda", torch.cuda.current_device())
     heap = SymmetricHeap(heap_bytes(T, H, F, world) + (64 << 20))
-    mlp = TpMlp(heap, T, H, F, cta_group=args.cta_group, gather_rows=args.gather_rows, fuse_silu=not args.no_fuse_silu)
+    mlp = TpMlp(heap, T, H, F, cta_group=args.cta_group, gather_rows=args.gather_rows, fuse_silu=not args.no_fuse_silu, graph=args.graph)
     x = torch.empty(T // world, H, dtype=torch.bfloat16, device=dev)
     ew.fill_normal_(x, seed=77 + rank)
     mlp.x_shard.copy_(x)
@@ -77,7 +78,11 @@ def main(argv=None) -> int:
         ref = baseline()
         torch.cuda.synchronize()
         max_rel = ((y.float() - ref.float()).abs() / (ref.float().abs() + 1)).max().item()
-    ser = C.timed_interleaved({"fused": mlp, "nccl": baseline}, args.iters, args.warmup, before=bar, flush=flush)
+    variants = {"fused": mlp, "nccl": baseline}
+    if args.graph:
+        mlp.capture()
+        variants["graph"] = mlp.replay
+    ser = C.timed_interleaved(variants, args.iters, args.warmup, before=bar, flush=flush)
     mlp.check()
     # stage breakdown of the fused path
     parts = C.timed_interleaved({"ag": mlp.ag, "silu": lambda: ew.silu_mul(hb, ab), "rs": mlp.rs},
@@ -94,10 +99,12 @@ def main(argv=None) -> int:
         print(f"# mlp_e2e tokens={T} hidden={H} ffn={F} tp={world} cta_group={args.cta_group} [{C.device_line()}]")
         print(f"fused {fused:.1f} us (p95 {mx('fused', 1):.1f}) = AG+GEMM{"+SiLU*mul" if mlp.fuse_silu else ""} {mx('ag'):.1f} + GEMM+RS {mx('rs'):.1f} (stages timed alone; stand-alone SiLU*mul kernel: {mx('silu'):.1f})")
         print(f"nccl+cublas {nccl:.1f} us | speedup {nccl / fused:.3f}x | roofline {roof:.1f} us ({100 * roof / fused:.1f} % of {r_ag['peaks']} peaks) | max rel diff {rel:.3g}")
+        if args.graph:
+            print(f"replayed from a CUDA graph: {mx('graph'):.1f} us (p95 {mx('graph', 1):.1f}), {fused / mx('graph'):.3f}x of the eager launches")
         csv = csvio.CsvAppender(args.csv, csvio.MLP_E2E_COLUMNS)
         csv.row(tokens=T, hidden=H, ffn=F, world=world, fused_us=fused, fused_p95=mx("fused", 1), ag_us=mx("ag"), silu_us=mx("silu"),
                 rs_us=mx("rs"), nccl_cublas_us=nccl, speedup=nccl / fused, roofline_us=roof, pct_roofline=100 * roof / fused,
-                max_rel_diff=rel, iters=args.iters, dtype="bf16")
+                max_rel_diff=rel, iters=args.iters, dtype="bf16", graph_us=(mx("graph") if args.graph else ""))
         csv.close()
     torch.cuda.synchronize()
     G.host_barrier()

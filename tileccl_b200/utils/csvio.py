@@ -51,7 +51,7 @@ P2P_CE_VS_TMA_COLUMNS = "method,tokens,hidden,bytes,avg_us,p50_us,p99_us,gbps,ve
 SYNC_COST_COLUMNS = "section,variant,payload_bytes,value,unit".split(",")
 # End-to-end MLP block (no counterpart in the reference).
 MLP_E2E_COLUMNS = ("tokens,hidden,ffn,world,fused_us,fused_p95,ag_us,silu_us,rs_us,nccl_cublas_us,speedup,"
-                   "roofline_us,pct_roofline,max_rel_diff,iters,dtype").split(",")
+                   "roofline_us,pct_roofline,max_rel_diff,iters,dtype,graph_us").split(",")
 
 
 class CsvAppender:
