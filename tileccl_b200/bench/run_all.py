@@ -168,7 +168,9 @@ def plan(n_gpus: int, quick: bool, out: Path, tuning: bool = False) -> list[tupl
         base = ["exp3_gemm_rs_fused", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it, "--order", "fused,nccl", "--csv", f"{o}/exp3_tuning.csv"]
         for tag, extra in (("default", []), ("st256", ["--st256"]), ("gm4", ["--group-m", "4"]), ("gm16", ["--group-m", "16"]), ("gm32", ["--group-m", "32"]),
                            ("chunks1", ["--rs-chunks", "1"]), ("chunks4", ["--rs-chunks", "4"]), ("ctas128", ["--num-ctas", "128"]), ("ctas96", ["--num-ctas", "96"]),
-                           ("cg1", ["--cta-group", "1"])):
+                           ("cg1", ["--cta-group", "1"]),
+                           # timing-only ablations (results invalid): where the time goes
+                           ("noreduce", ["--ablate", "1"]), ("nosignal", ["--ablate", "2"]), ("nocomm_warps", ["--ablate", "3"])):
             steps.append((f"tune_rs_{tag}", launch + base + extra, 600, 2))
     steps.append(("mlp_e2e", launch + ["mlp_e2e", "--iters", "10" if quick else "50", "--verify", "--csv", f"{o}/mlp_e2e.csv"], 900, 1))
     steps.append(("bench", [py, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={max(1, n_gpus)}", "--master-addr", "127.0.0.1", "--master-port", "29571",
