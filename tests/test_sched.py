@@ -81,3 +81,20 @@ def test_ag_push_order_follows_arrival():
         # then tile row i of every peer before tile row i + 1 of any peer
         assert [m % seg_tiles for m in rest] == [i for i in range(seg_tiles) for _ in range(world - 1)]
         assert {m // seg_tiles for m in rest[:world - 1]} == set(range(world)) - {r}
+
+
+def test_rs_order_spreads_the_tiles_in_flight_over_all_owners():
+    """GEMM+RS at the headline shape (128 tile rows x 32 tile columns, 74 CTA pairs): whatever 74 consecutive
+    tiles are in flight, every owner receives the same share of them (+-1), so no rank's ingress is a hot spot."""
+    from collections import Counter
+    m_tiles, n_tiles, in_flight = 128, 32, 74
+    for world in (2, 4, 8):
+        st = m_tiles // world
+        group_m = world * max(1, 8 // world)            # the plan's default raster group: one round of owners
+        for rank in (0, world - 1):
+            tiles = tiling.schedule(m_tiles, n_tiles, group_m, tiling.ORDER_RS_PUSH, world, rank, st)
+            for t0 in range(0, len(tiles) - in_flight, 7):
+                c = Counter(m // st for m, _ in tiles[t0:t0 + in_flight])
+                assert max(c.values()) - min(c.get(o, 0) for o in range(world)) <= 1, (world, rank, t0, c)
+            # the own segment is the last step of every round
+            assert all(tiles[i][0] // st == rank for i in range(world - 1, group_m, world))
