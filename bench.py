@@ -295,6 +295,9 @@ def main():
             "pct_roofline": round(100.0 * roof_us / step_us, 1),
             "pct_roofline_gemm_rs": round(100.0 * roof_rs["roofline_us"] / rs_us, 1),
             "pct_roofline_ag_gemm": round(100.0 * roof_ag["roofline_us"] / ag_us, 1),
+            "wave_efficiency": {"gemm_rs": round(roofline.wave_efficiency(M, N_rs, args.cta_group)["efficiency"], 4),
+                                "ag_gemm": round(roofline.wave_efficiency(M, N_ag, args.cta_group)["efficiency"], 4),
+                                "note": "share of the persistent grid's tile slots that hold a tile; not folded into the roofline"},
             "verified": verified, "verify_errors": errs,
             "clocks": clocks, "e2e": e2e, "gpu_launches": gpu_launches, "impl": "tileccl_b200",
         }

@@ -64,3 +64,10 @@ def test_clock_summary_flags_throttling():
     assert s["samples"] == 4 and s["sm_max_mhz"] == 1965 and s["sm_mhz"] in (1380.0, 1400.0)
     assert "sw_power_cap" in s["reasons"] and "hw_thermal_slowdown" in s["reasons"]
     assert clocks.summarize([])["sm_mhz"] is None
+
+
+def test_wave_efficiency_of_the_persistent_grid():
+    w = roofline.wave_efficiency(32768, 8192, cta_group=2, sms=148)        # GEMM+RS headline shape
+    assert (w["tiles"], w["groups"], w["waves"]) == (4096, 74, 56) and abs(w["efficiency"] - 4096 / (56 * 74)) < 1e-12
+    assert roofline.wave_efficiency(256 * 74, 256)["efficiency"] == 1.0     # exactly one full wave
+    assert roofline.wave_efficiency(128, 256, cta_group=1)["efficiency"] == 1 / 148

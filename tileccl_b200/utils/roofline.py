@@ -50,3 +50,17 @@ def ag_gemm_roofline_us(M: int, N_local: int, K: int, world: int, sustained: boo
     t_c = flops / (tf * 1e12) * 1e6
     t_l = link_bytes / (NVLINK_GBS_PER_DIR * 1e9) * 1e6
     return {"compute_us": t_c, "link_us": t_l, "roofline_us": max(t_c, t_l), "peaks": pk["source"]}
+
+
+def wave_efficiency(M: int, N: int, cta_group: int = 2, sms: int = 148) -> dict:
+    """Share of the persistent grid's tile slots that hold a tile: ``tiles / (waves * groups)``.
+
+    The kernels run one CTA (or CTA pair) per SM over a static list of 128*cta_group x 256 tiles, so
+    the last wave is partly empty unless the tile count divides by the number of groups.  This loss is
+    part of the distance to the roofline that no kernel tuning removes (the roofline figures above do
+    not include it)."""
+    tile_m = 128 * cta_group
+    tiles = -(-M // tile_m) * -(-N // 256)
+    groups = max(1, sms // cta_group)
+    waves = -(-tiles // groups)
+    return {"tiles": tiles, "groups": groups, "waves": waves, "efficiency": tiles / (waves * groups)}
