@@ -13,7 +13,7 @@ import sys
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 EXPERIMENTS = ("exp1_ce_interference", "exp2_ag_gemm_granularity", "exp3_epilogue_remote",
-               "exp3_gemm_rs_fused", "mlp_e2e", "nvls_bw", "gemm_vs_cublas", "once")
+               "exp3_gemm_rs_fused", "mlp_e2e", "nvls_bw", "gemm_vs_cublas", "once", "tune_gemm_rs")
 
 
 def main() -> int:
