@@ -89,3 +89,20 @@ def test_tuning_summary_sorts_knob_settings(tmp_path):
     lines = [line for line in txt.splitlines() if "st256=" in line]
     assert len(lines) == 2 and "st256=1" in lines[0] and "700.0" in lines[0] and "1.143x of default" in lines[0]
     assert "1.000x of default" in lines[1] and "1.500x of NCCL+cuBLAS" in lines[1]
+
+
+def test_sweep_settings_match_the_op_and_the_analyser():
+    """Every setting of the sweep driver is a keyword of GemmRs, and its knobs string is what the analyser
+    recognises as the default."""
+    import inspect
+
+    from tileccl_b200.bench import tune_gemm_rs
+    from tileccl_b200.ops.gemm_rs import GemmRs
+    params = set(inspect.signature(GemmRs.__init__).parameters)
+    for name, kw in tune_gemm_rs.SETTINGS.items():
+        assert set(kw) <= params, name
+    assert tune_gemm_rs.knobs_string({}) == "cta_group=2|transport=p2p|rs_chunks=0|group_m=0|num_ctas=0|st256=0|ablate=0"
+    rows = [{"max_over_ranks_us": "800", "nccl_cublas_us": "1200", "knobs": tune_gemm_rs.knobs_string({})},
+            {"max_over_ranks_us": "760", "nccl_cublas_us": "1200", "knobs": tune_gemm_rs.knobs_string({"st256": True})}]
+    txt = analyze.tuning_summary(rows)
+    assert "1.053x of default" in txt and txt.index("st256=1") < txt.index("st256=0")
