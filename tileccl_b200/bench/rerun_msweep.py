@@ -20,6 +20,9 @@ from . import run_all
 
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
+    if "-h" in argv or "--help" in argv:
+        print(__doc__)
+        print("Other flags are those of run_all:\n")
     full = "--full" in argv
     argv = [a for a in argv if a != "--full"]
     if "--out" not in argv and "--resume" not in argv:
