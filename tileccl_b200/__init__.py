@@ -15,5 +15,8 @@ def _register():
 try:
     _t = _register()
     init, shutdown, symm_empty, heap, check_all = _t.init, _t.shutdown, _t.symm_empty, _t.heap, _t.check_all
-except (ImportError, AttributeError):  # torch missing or too old for torch.library: the C++ programs and the ctypes layer still work
-    pass
+except (ImportError, AttributeError, RuntimeError) as _e:
+    # torch missing or too old for torch.library (or the op namespace taken): the C++ programs and the ctypes
+    # layer still work, the torch.ops layer does not
+    import warnings
+    warnings.warn(f"tileccl_b200: torch.ops.tileccl is unavailable ({type(_e).__name__}: {_e})")
