@@ -23,7 +23,9 @@
 //   warp 0      TMA producer (one lane)
 //   warp 1      TMEM allocation + tcgen05.mma issue (one lane, leader CTA only)
 //   warps 2-5   epilogue: tcgen05.ld -> bf16 -> swizzled smem transpose ->
-//               coalesced 16-byte global stores, 256 contiguous bytes per row (local or peer)
+//               coalesced 16-byte global stores, 256 contiguous bytes per row (local or peer);
+//               options: 32-byte stores (epi_st256), TMA stores from the same buffer (epi_tma_store),
+//               SiLU(gate)*up on the accumulators (epi_silu_mul)
 //   warps 6-9   communication: reduce warps (GEMM+RS) or gather warps (AG+GEMM)
 //   warp 10     GEMM+RS signalling: publishes finished tiles to their owners
 //
@@ -32,10 +34,16 @@
 // leader issues cta_group::2 MMAs that read both CTAs' shared memory, and each
 // CTA drains its own 128 accumulator rows.
 //
-// No TMA instruction here touches another GPU's memory: remote data moves by
-// plain ld/st only.  Every wait is bounded (deadline from %globaltimer); on
+// No TMA load here touches another GPU's memory, and in the fused modes no TMA
+// instruction at all does: remote data moves by plain ld/st.  (The optional
+// TMA-store epilogue of the plain mode stores wherever D lives, a peer included:
+// that is the epilogue-remote experiment's second epilogue.)  Every wait is bounded (deadline from %globaltimer); on
 // time-out the CTA records a status word, lets its copies land, frees its TMEM
 // and returns.
+//
+// The call number that the flag counters are compared with comes from the host with every
+// launch, or from a device word that the kernel advances itself (GemmParams::epoch_dev), which
+// lets a captured CUDA graph replay the launch.
 //
 // Reference parity: comm_comp/gemm_sm90.cuh:48-140 (plain GEMM, TMA-store and
 // direct-store epilogues), comm_comp/rs_gemm_kernel_sm90.cuh:90-892 and
