@@ -60,3 +60,17 @@ def test_platform_file_round_trip(tmp_path):
     f.write_text(json.dumps({"warp_drive": 1}))
     with pytest.raises(ValueError):
         S.Platform.from_json(str(f))
+
+
+def test_shipped_platform_files_reproduce_the_reference_table():
+    """The parameter files load, and the selector gives the rows of the reference's decision table for its two
+    machines (tests/ANALYSIS.md:118-128): L2-sensitive compute on H20 -> copy engine; an HBM-heavy phase on the
+    PCIe pair where the transfer's latency matters -> an SM mover (S_m 1.01 against 1.41 for the copy engine)."""
+    b200 = S.load_platform("b200_nvswitch")
+    assert b200.ce_gbps == S.Platform().ce_gbps and "measured" in b200.notes
+    h20 = S.load_platform("h20_nvlink_reference")
+    r = S.choose(h20, 64 << 20, compute_us=2000.0, bound="l2")
+    assert r["best"] == "ce" and r["table"]["reg"]["compute_us"] > 1.8 * 2000
+    pcie = S.load_platform("rtx_pcie5_reference")
+    r = S.choose(pcie, 64 << 20, compute_us=100.0, bound="hbm")          # transfer-bound: its own slow-down decides
+    assert r["best"] in ("reg", "bulk") and r["table"]["ce"]["comm_us"] > 1.2 * r["table"]["reg"]["comm_us"]

@@ -9,7 +9,8 @@ The parameters are the figures this suite measured on 8 x B200 (``reports/REPORT
 runs): ``pk_bw_sweep`` (link bandwidth per mover, SMs to saturate, per-copy cost of the copy engine),
 ``p2p_ce_vs_tma`` (one-shot latencies), ``sync_cost`` (one-way latency, cost of a release flag),
 ``interference_matrix`` / ``exp1_ce_interference`` (what a transfer costs a concurrent kernel).
-Another platform overrides them with ``Platform.from_json``.
+Another platform overrides them with ``Platform.from_json``; ``utils/platforms/`` holds this B200 vector and,
+for comparison, the two machines of the reference filled in from the figures it publishes.
 
 The model is the zero-parameter one the reference validates with ``pipeline_e2e``:
 a pipelined producer -> transfer -> consumer takes ``max(Tc_src, Tm, Tc_dst)``; a transfer takes
@@ -27,6 +28,7 @@ TRANSPORTS = ("ce", "reg", "bulk", "fused_st", "fused_pull")
 @dataclass
 class Platform:
     name: str = "B200 NVLink5 NVSwitch"
+    notes: str = ""                   # where the figures come from, which ones are placeholders
     sms: int = 148
     # link bandwidth per direction, GB/s
     ce_gbps: float = 749.0            # copy engine, 128 MB copy
@@ -73,6 +75,12 @@ class Platform:
     def to_json(self, path: str) -> None:
         with open(path, "w") as f:
             json.dump(asdict(self), f, indent=1)
+
+
+def load_platform(name: str) -> Platform:
+    """A parameter file shipped with the package (``b200_nvswitch``, ``h20_nvlink_reference``, ``rtx_pcie5_reference``)."""
+    import os
+    return Platform.from_json(os.path.join(os.path.dirname(os.path.abspath(__file__)), "platforms", name + ".json"))
 
 
 def transfer_us(p: Platform, transport: str, nbytes: int, n_msgs: int = 1, sms: int = 16) -> float:
