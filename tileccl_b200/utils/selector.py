@@ -12,6 +12,11 @@ runs): ``pk_bw_sweep`` (link bandwidth per mover, SMs to saturate, per-copy cost
 Another platform overrides them with ``Platform.from_json``; ``utils/platforms/`` holds this B200 vector and,
 for comparison, the two machines of the reference filled in from the figures it publishes.
 
+Limits: the link figures are those of one transfer between one pair of GPUs.  When every GPU sends to
+every other at once the copy engines reach less (462 GB/s per GPU in exp1's 56-leg all-gather pattern),
+and the model knows nothing of data dependencies: a transfer that must wait for a kernel's tiles is not
+"independent".  It ranks transports for a planner; it does not replace measuring the fused kernel.
+
 The model is the zero-parameter one the reference validates with ``pipeline_e2e``:
 a pipelined producer -> transfer -> consumer takes ``max(Tc_src, Tm, Tc_dst)``; a transfer takes
 ``start + n_msgs * per_message + bytes / bandwidth``; a transport that occupies SMs slows an SM-bound
@@ -137,3 +142,33 @@ def choose(p: Platform, nbytes: int, n_msgs: int = 1, compute_us: float = 0.0, b
         table[t] = {"comm_us": comm, "compute_us": comp, "total_us": max(comm, comp)}
     best = min(table, key=lambda k: (table[k]["total_us"], table[k]["comm_us"]))
     return {"best": best, "table": table}
+
+
+def main(argv=None) -> int:
+    """``python -m tileccl_b200.utils.selector --bytes 64M [--msgs N] [--compute-us T --bound tensor|hbm|l2]
+    [--fused] [--sms 16] [--platform NAME|FILE.json]`` prints the ranking."""
+    import argparse
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--bytes", required=True)
+    ap.add_argument("--msgs", type=int, default=1)
+    ap.add_argument("--compute-us", type=float, default=0.0)
+    ap.add_argument("--bound", default="tensor", choices=["tensor", "hbm", "l2"])
+    ap.add_argument("--fused", action="store_true", help="the producing or consuming kernel can carry the transfer")
+    ap.add_argument("--sms", type=int, default=16, help="SMs a mover kernel may take")
+    ap.add_argument("--platform", default="b200_nvswitch")
+    a = ap.parse_args(argv)
+    mult = {"K": 1 << 10, "M": 1 << 20, "G": 1 << 30}
+    txt = a.bytes.strip().upper().rstrip("B")
+    nbytes = int(float(txt[:-1]) * mult[txt[-1]]) if txt and txt[-1] in mult else int(txt)
+    p = Platform.from_json(a.platform) if a.platform.endswith(".json") else load_platform(a.platform)
+    r = choose(p, nbytes, a.msgs, a.compute_us, a.bound, a.fused, a.sms)
+    print(f"# {p.name}: {nbytes} bytes in {a.msgs} message(s)" + (f", beside a {a.bound}-bound kernel of {a.compute_us:.0f} us" if a.compute_us else ""))
+    print(f"{'transport':12s} {'comm us':>10s} {'compute us':>11s} {'total us':>10s}")
+    for t, v in sorted(r["table"].items(), key=lambda kv: kv[1]["total_us"]):
+        print(f"{t:12s} {v['comm_us']:10.1f} {v['compute_us']:11.1f} {v['total_us']:10.1f}" + ("   <- best" if t == r["best"] else ""))
+    return 0
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(main())
