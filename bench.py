@@ -7,7 +7,10 @@ N GPUs) followed by one fused AG+GEMM (A shard [32768/N, 8192], local B
 [8192, 28672/N]); bf16 N(0,1) activations, N(0,0.02) AG weights, synthetic.
 The same step is also timed on the baseline path (torch.matmul = cuBLAS, then /
 preceded by the NCCL collective).  Every time is device-timed with CUDA events
-and reported as the max over ranks; the L2 is flushed between timed steps.
+and reported as the max over ranks.  Ahead of every timed operation (of both paths) the L2 is flushed and a
+device barrier over all ranks runs, untimed, so that an operation's time does not include waiting for a rank
+that was still busy with the previous one (the reference times its fused kernel the same way:
+comm_comp/exp3_gemm_rs_fused.cu:278-331).
 
     python bench.py --gpus 1 --steps 20 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \\
@@ -41,6 +44,8 @@ def parse_args():
     ap.add_argument("--n-ag", type=int, default=28672, help="global N of the AG+GEMM, sharded over the GPUs")
     ap.add_argument("--gather-rows", type=int, default=512)
     ap.add_argument("--cta-group", type=int, default=2)
+    ap.add_argument("--pre-barrier", type=int, default=1, help="1: a device barrier over all ranks runs (untimed) ahead of every timed operation; "
+                                                                "0: operations follow each other directly and rank skew is charged to the next one")
     ap.add_argument("--no-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -119,25 +124,66 @@ def main():
         def base_ag():
             return base.ag_gemm_baseline(shard_b, Bt_ag, gathered=gathered, out=out_ag_b)
 
-    # ---- verification (untimed): fused vs baseline on the full outputs ----
+    # ---- verification (untimed) ----
+    # GEMM+RS: against an fp32 computation of sampled rows of this rank's shard (every 16th row: all tile rows,
+    # all four epilogue warps, every tile column).  Each rank's partial product crosses NVLink as bf16 and the
+    # sum is rounded once more, so |out - ref| <= 2^-8 * (sum_r |partial_r| + |ref|) (+5 % and a small absolute
+    # term for the fp32 reference's own rounding).  AG+GEMM: against cuBLAS on the NCCL-gathered input.
     verified = None
     fused_step()
     rs.check()
     ag.check()
+    seg = M // tp
+    rows_local = torch.arange(0, seg, 16, device=dev)
+    if tp > 1:
+        want_rows = torch.cat([r * seg + rows_local for r in range(tp)])            # every rank's sample, in rank order
+        a_rows = [torch.empty(want_rows.numel(), K_rs, dtype=torch.bfloat16, device=dev) for _ in range(tp)]
+        b_all = [torch.empty_like(Bt_rs) for _ in range(tp)]
+        dist.all_gather(a_rows, A_rs[want_rows].contiguous())
+        dist.all_gather(b_all, Bt_rs)
+        mine = slice(rank * rows_local.numel(), (rank + 1) * rows_local.numel())
+        parts = [a[mine].float() @ b.float().t() for a, b in zip(a_rows, b_all)]
+        del a_rows, b_all
+    else:
+        parts = [A_rs[rows_local].float() @ Bt_rs.float().t()]
+    ref = sum(parts)
+    bound = 1.05 * 2.0 ** -8 * (sum(p.abs() for p in parts) + ref.abs()) + 1e-2
+    got = rs.out[rows_local].float()
+    e_rs = ((got - ref).abs() / bound).max().item()                                  # <= 1 passes
+    e_rs_rel = ((got - ref).abs() / (ref.abs() + 1)).max().item()
+    del parts, ref, bound, got
+    errs = {"gemm_rs_err_over_bf16_rounding_bound": e_rs, "gemm_rs_max_rel": e_rs_rel}
+    ok_local = e_rs <= 1.0
     if run_base:
-        ob = base_rs()
         oa = base_ag()
         torch.cuda.synchronize()
-        # bf16 partials/NCCL both round at the partials' magnitude: compare on that scale.
-        scale = float(K_rs * tp) ** 0.5
-        e_rs = ((rs.out.float() - ob.float()).abs().max() / scale).item()
         e_ag = ((ag.out.float() - oa.float()).abs() / (oa.float().abs() + 1)).max().item()
-        verified = bool(e_rs < 0.05 and e_ag < 0.02)
-        errs = {"gemm_rs_max_abs_over_sqrtK": e_rs, "ag_gemm_max_rel": e_ag}
+        errs["ag_gemm_max_rel_vs_cublas"] = e_ag
+        ok_local = ok_local and e_ag < 0.02
     else:
-        errs = {}
+        if tp > 1:
+            shards = [torch.empty_like(ag.a_shard) for _ in range(tp)]
+            dist.all_gather(shards, ag.a_shard.contiguous())
+            full_x = torch.cat(shards)
+            del shards
+        else:
+            full_x = ag.a_full
+        sample = torch.arange(0, M, 64, device=dev)
+        ref_ag = full_x[sample].float() @ Bt_ag.float().t()
+        e_ag = ((ag.out[sample].float() - ref_ag).abs() / (ref_ag.abs() + 1)).max().item()
+        errs["ag_gemm_max_rel_vs_fp32_rows"] = e_ag
+        ok_local = ok_local and e_ag < 0.02
+    verified = bool(G.max_over_ranks(0.0 if ok_local else 1.0) == 0.0)
+    errs = {k: G.max_over_ranks(v) for k, v in errs.items()}
 
     flush = L2Flusher()
+
+    bar = ew.DeviceBarrier(heap)
+
+    def before_op():
+        flush()
+        if args.pre_barrier:
+            bar()
 
     def timed(variants, n_steps, n_warm):
         """variants: {name: [fn, ...]}.  Per-step device times (us) of each
@@ -147,22 +193,25 @@ def main():
         for _ in range(n_warm):
             for n in names:
                 for f in variants[n]:
+                    before_op()
                     f()
         torch.cuda.synchronize()
         G.host_barrier()
-        ev = {n: [[torch.cuda.Event(enable_timing=True) for _ in range(len(variants[n]) + 1)]
+        own0 = rs.launches + ag.launches + bar.epoch          # kernels of this library launched so far
+        ev = {n: [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in variants[n]]
                   for _ in range(n_steps)] for n in names}
         for i in range(n_steps):
             for n in names:
-                flush()
-                ev[n][i][0].record()
                 for j, f in enumerate(variants[n]):
+                    before_op()
+                    ev[n][i][j][0].record()
                     f()
-                    ev[n][i][j + 1].record()
+                    ev[n][i][j][1].record()
         torch.cuda.synchronize()
         G.host_barrier()
-        return {n: [[ev[n][i][j].elapsed_time(ev[n][i][j + 1]) * 1e3 for i in range(n_steps)]
-                    for j in range(len(variants[n]))] for n in names}
+        own = rs.launches + ag.launches + bar.epoch - own0   # fused kernels and device barriers inside the timed loop
+        return {n: [[ev[n][i][j][0].elapsed_time(ev[n][i][j][1]) * 1e3 for i in range(n_steps)]
+                    for j in range(len(variants[n]))] for n in names}, own
 
     variants = {"fused": [rs, ag]}
     if run_base:
@@ -174,9 +223,7 @@ def main():
         if rank == 0:
             phys = int(os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")[local]) if os.environ.get("CUDA_VISIBLE_DEVICES", "").replace(",", "").isdigit() else local
             sampler = make_sampler(phys).start()
-        launches0 = rs.launches + ag.launches
-        res = timed(variants, steps, warmup)
-        gpu_launches = rs.launches + ag.launches - launches0 - 2 * warmup
+        res, gpu_launches = timed(variants, steps, warmup)
         clocks = sampler.summary() if sampler else None
         throttled = torch.tensor([1 if clocks and bad_reasons & set(clocks.get("reasons", [])) else 0], device=dev)
         if world > 1:
@@ -190,6 +237,7 @@ def main():
         clocks["attempts"] = attempt + 1
     rs.check()
     ag.check()
+    bar.check()
     per = res["fused"]
     rs_us = G.max_over_ranks(sum(per[0]) / steps)
     ag_us = G.max_over_ranks(sum(per[1]) / steps)
@@ -267,9 +315,14 @@ def main():
 
     roof_rs = roofline.gemm_rs_roofline_us(M, N_rs, K_rs, tp)
     roof_ag = roofline.ag_gemm_roofline_us(M, N_ag, K_ag, tp)
-    roof_us = roof_rs["roofline_us"] + roof_ag["roofline_us"]
     flops = 2.0 * M * N_rs * K_rs * tp + 2.0 * M * N_ag * K_ag * tp
+    # Which cuBLAS peak bounds this run depends on the clock it held: both fractions are given, `pct` is the one that applies.
+    f_rs = roofline.fractions(roof_rs, rs_us, clocks)
+    f_ag = roofline.fractions(roof_ag, ag_us, clocks)
+    which = "burst" if "burst" in (f_rs["of"], f_ag["of"]) else "sustained"
+    roof_us = (roof_rs["roofline_burst_us"] + roof_ag["roofline_burst_us"]) if which == "burst" else (roof_rs["roofline_us"] + roof_ag["roofline_us"])
 
+    rc = 0
     if rank == 0:
         out = {
             "metric": "fused GEMM+RS + AG+GEMM step time (device-timed, max over ranks)",
@@ -280,8 +333,9 @@ def main():
                        "gemm_rs": {"M": M, "N": N_rs, "K_global": args.k_rs, "K_per_rank": K_rs},
                        "ag_gemm": {"M": M, "K": K_ag, "N_global": args.n_ag, "N_per_rank": N_ag, "gather_rows": args.gather_rows},
                        "global_batch": M, "seq_len": None, "parallelism": f"tp{tp}", "cta_group": args.cta_group,
-                       "l2": "flushed between timed steps (256 MiB write); inputs also exceed L2",
-                       "timing": "fused and NCCL+cuBLAS steps alternate inside one timed loop"},
+                       "l2": "flushed ahead of every timed operation (256 MiB write); inputs also exceed L2",
+                       "timing": ("fused and NCCL+cuBLAS steps alternate inside one timed loop; a step is the sum of its two operations, each timed by "
+                                  "its own pair of CUDA events" + (", behind an untimed device barrier over all ranks" if args.pre_barrier else ""))},
             "gemm_rs_us": round(rs_us, 2), "ag_gemm_us": round(ag_us, 2),
             "nccl_cublas_us": None if b_step_us is None else round(b_step_us, 2),
             "nccl_cublas_gemm_rs_us": None if b_rs_us is None else round(b_rs_us, 2),
@@ -291,22 +345,32 @@ def main():
             "speedup_ag_gemm": None if b_ag_us is None else round(b_ag_us / ag_us, 4),
             "tflops_aggregate": round(flops / (step_us * 1e-6) / 1e12, 1),
             "roofline_us": round(roof_us, 2),
-            "roofline": {"gemm_rs": roof_rs, "ag_gemm": roof_ag, "of": roof_rs["peaks"] + " (sustained cuBLAS bf16, 770 GB/s NVLink per direction)"},
+            "roofline": {"gemm_rs": roof_rs, "ag_gemm": roof_ag,
+                         "of": f"{roof_rs['peaks']} peaks: cuBLAS bf16 {which} rate (chosen from the SM clock sampled under load), "
+                               f"{roof_rs['link_gbs']:.0f} GB/s NVLink per direction ({roof_rs['link_file']})"},
             "pct_roofline": round(100.0 * roof_us / step_us, 1),
-            "pct_roofline_gemm_rs": round(100.0 * roof_rs["roofline_us"] / rs_us, 1),
-            "pct_roofline_ag_gemm": round(100.0 * roof_ag["roofline_us"] / ag_us, 1),
+            "pct_roofline_gemm_rs": f_rs["pct"], "pct_roofline_ag_gemm": f_ag["pct"],
+            "pct_roofline_detail": {"gemm_rs": f_rs, "ag_gemm": f_ag},
             "wave_efficiency": {"gemm_rs": round(roofline.wave_efficiency(M, N_rs, args.cta_group)["efficiency"], 4),
                                 "ag_gemm": round(roofline.wave_efficiency(M, N_ag, args.cta_group)["efficiency"], 4),
                                 "note": "share of the persistent grid's tile slots that hold a tile; not folded into the roofline"},
             "verified": verified, "verify_errors": errs,
             "clocks": clocks, "e2e": e2e, "gpu_launches": gpu_launches, "impl": "tileccl_b200",
         }
+        if not verified:
+            # A wrong result is not a measurement: no value, and a failing exit code.
+            out["invalid"] = "verification failed: " + json.dumps(errs)
+            for k in ("value", "ms_per_step", "gemm_rs_us", "ag_gemm_us", "speedup_vs_nccl_cublas", "speedup_gemm_rs", "speedup_ag_gemm", "pct_roofline"):
+                out[k] = None
+            out["e2e"] = None
         print(json.dumps(out), flush=True)
+    if not verified:
+        rc = 3
     torch.cuda.synchronize()
     G.host_barrier()
     heap.close()
     G.shutdown()
-    return 0
+    return rc
 
 
 if __name__ == "__main__":

@@ -1,6 +1,4 @@
 """tcgen05 GEMM kernels vs a plain PyTorch fp32 reference (single GPU)."""
-import os
-
 import pytest
 import torch
 
@@ -112,12 +110,6 @@ def test_plain_gemm_32_byte_stores(native_lib, cta_group):
     assert torch.equal(got, want)
 
 
-# Paths that compile but have not run on a GPU yet are first run alone, with TILECCL_TEST_UNVERIFIED=1.
-unverified = pytest.mark.skipif(os.environ.get("TILECCL_TEST_UNVERIFIED") != "1",
-                                reason="not yet run on a GPU: run it alone first with TILECCL_TEST_UNVERIFIED=1")
-
-
-@unverified
 @pytest.mark.parametrize("cta_group", [1, 2])
 def test_plain_gemm_tma_store_epilogue(native_lib, cta_group):
     """cp.async.bulk.tensor stores from the staging buffer give the same bits as st.global, also with row
@@ -260,7 +252,6 @@ def test_torch_op_layer_single_gpu(native_lib):
         tc.shutdown()
 
 
-@unverified
 def test_fused_ops_replay_from_a_cuda_graph(native_lib):
     """With the call number kept in device memory the fused kernels can be captured once and replayed:
     epochs advance on the device, counters are never reset, results stay right."""
@@ -296,3 +287,77 @@ def test_fused_ops_replay_from_a_cuda_graph(native_lib):
         assert rs.plan.epoch == 3 + i
         rs.audit()
     heap.close()
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_gemm_rs_publishes_a_tile_only_after_all_four_warps_stored_it(native_lib, cta_group):
+    """One epilogue warp is made to lag by several microseconds per tile (after it has handed the accumulator
+    back), so the other three run a tile or two ahead.  The staging buffer is poisoned with NaN before every
+    call: if a tile were published to the reduce warps before the slow warp's 32 rows are stored, NaNs (or the
+    previous call's rows) would reach the output.  Many tiles per CTA, so that the lead builds up."""
+    from tileccl_b200.ops.gemm_rs import GemmRs
+    from tileccl_b200.parallel.heap import SymmetricHeap
+    torch.manual_seed(41)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    M, N, K = 128 * cta_group * 8, 256 * (sms // cta_group), 128      # 8 tiles per CTA (or CTA pair), short mainloop
+    heap = SymmetricHeap(2 * M * N * 2 + (16 << 20))
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    ref = _ref(A, Bt)
+    op = GemmRs(heap, A, Bt, cta_group=cta_group, force_staged=True, timeout_ms=2000, ablate=8)
+    for _ in range(3):
+        op.stage.fill_(float("nan"))
+        op.out.fill_(float("nan"))
+        out = op()
+        op.check()
+        assert not torch.isnan(out).any()
+        assert _rel(out, ref) < 1e-2
+    heap.close()
+
+
+def test_plan_set_operands_repoints_a_cached_plan(native_lib):
+    """A plan re-pointed at new operands of the same layout reads the new ones and keeps no reference."""
+    import gc
+    import weakref
+    from tileccl_b200.ops.gemm import GemmPlan
+    torch.manual_seed(43)
+    A = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16)
+    Bt = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16)
+    plan = GemmPlan(A, Bt, cta_group=2, timeout_ms=1000, hold_operands=False)
+    assert _rel(plan(), _ref(A, Bt)) < 1e-2
+    wr = weakref.ref(A)
+    A2 = torch.randn_like(A)
+    B2 = torch.randn_like(Bt)
+    plan.set_operands(A2, B2)
+    del A
+    gc.collect()
+    assert wr() is None                       # the plan did not keep the first activation alive
+    assert _rel(plan(), _ref(A2, B2)) < 1e-2
+    plan.check()
+    with pytest.raises(ValueError):
+        plan.set_operands(A2[:256], B2)
+
+
+def test_torch_ops_reuse_one_plan_for_fresh_activations(native_lib):
+    """A loop that allocates a new activation every step must reuse one plan (and one staging buffer): the
+    symmetric heap's cursor does not move after the first call."""
+    import tileccl_b200 as tc
+    torch.manual_seed(44)
+    Bt = torch.randn(512, 384, device="cuda", dtype=torch.bfloat16)
+    h = tc.init(128 << 20)
+    try:
+        keep = []
+        cursor = None
+        for i in range(6):
+            A = torch.randn(512, 384, device="cuda", dtype=torch.bfloat16)
+            keep.append(A)                    # keeps every address distinct
+            y = torch.ops.tileccl.gemm_rs(A, Bt)
+            assert _rel(y, _ref(A, Bt)) < 1e-2
+            z = torch.ops.tileccl.gemm(A, Bt)
+            assert _rel(z, _ref(A, Bt)) < 1e-2
+            if i == 0:
+                cursor = h._cursor
+            assert h._cursor == cursor
+        tc.check_all()
+    finally:
+        tc.shutdown()

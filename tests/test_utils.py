@@ -53,6 +53,21 @@ def test_roofline_headline_shapes():
     assert roofline.gemm_rs_roofline_us(1024, 1024, 1024, 1)["link_us"] == 0
 
 
+def test_roofline_fraction_follows_the_clock_the_run_held():
+    r = roofline.ag_gemm_roofline_us(32768, 14336, 8192, 2)
+    assert r["roofline_burst_us"] <= r["roofline_us"] and r["link_file"].endswith(".json")
+    fast = {"sm_mhz": 1965.0, "sm_max_mhz": 1965.0}
+    slow = {"sm_mhz": 1350.0, "sm_max_mhz": 1965.0}
+    assert roofline.pick_peak(fast) == "burst" and roofline.pick_peak(slow) == "sustained" and roofline.pick_peak(None) == "sustained"
+    t = r["roofline_us"] * 0.99               # faster than the sustained roofline: a run that held a high clock
+    f = roofline.fractions(r, t, slow)
+    assert f["of"] == "burst" and f["pct"] <= 100.0 and f["pct_sustained"] > 100.0
+    f2 = roofline.fractions(r, r["roofline_us"] * 1.25, slow)
+    assert f2["of"] == "sustained" and f2["pct"] == pytest.approx(80.0)
+    assert roofline.fractions(r, r["roofline_us"] * 1.25, fast)["of"] == "burst"
+    assert roofline.fractions(r, 0.0)["pct"] is None
+
+
 def test_clock_summary_flags_throttling():
     text = "\n".join([
         "0, 1965, 1965, 250.0, 0x0, Not Active, Not Active, Not Active, Not Active",

@@ -110,6 +110,7 @@ def lib() -> C.CDLL:
     check_desc_layout(L)
     sig("tcl_gemm_plan_create", vp, [C.POINTER(GemmDesc), C.c_char_p, i32])
     sig("tcl_gemm_plan_run", i32, [vp, i32, vp])
+    sig("tcl_gemm_plan_set_operands", i32, [vp, vp, vp])
     sig("tcl_gemm_plan_destroy", None, [vp])
     sig("tcl_gemm_plan_grid", i32, [vp])
     sig("tcl_gemm_plan_launches", i32, [vp])

@@ -99,8 +99,10 @@ struct GemmParams {
   int epi_tma_store;  // the plain epilogue leaves through TMA: cp.async.bulk.tensor stores of 32 x 64 boxes from the
                       // warp's staging buffer (not with GEMM+RS communication, not with epi_silu_mul)
   int epi_st256;  // the plain epilogue stores 32 bytes per lane (st.global.v8.b32); needs 32-byte aligned destinations and pitch
-  int ablate;     // experiment knobs (timing only): bit 0 = no reduce warps, bit 1 = no tile signals,
-                  // bit 2 = AG+GEMM producer does not wait for gathered rows
+  int ablate;     // experiment knobs: bit 0 = no reduce warps, bit 1 = no tile signals, bit 2 = AG+GEMM producer
+                  // does not wait for gathered rows (these three: timing only, the output is not valid);
+                  // bit 3 = the last epilogue warp sleeps a few microseconds before the final stores of every
+                  // tile (the output stays valid: a test of the publish-after-all-stores rule)
 
   // Output routing.  Rows are split in segments of seg_rows; row r of segment
   // s goes to dst_base[s] + (dst_row_off[s] + r - s * seg_rows) * ldc.
@@ -295,7 +297,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
   volatile uint32_t* s_tmem_ptr = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * Cfg::STAGES + 40);
   volatile int* s_abort = reinterpret_cast<volatile int*>(ctrl + 16 * Cfg::STAGES + 44);
   volatile int* s_bcast = reinterpret_cast<volatile int*>(ctrl + 16 * Cfg::STAGES + 48);
-  int* s_warps_done = reinterpret_cast<int*>(ctrl + 16 * Cfg::STAGES + 52);  // epilogue warp-tiles stored
+  // tiles whose stores epilogue warp w has issued, one monotonic counter per warp (GEMM+RS): a tile may be
+  // published once the smallest of the four has passed it
+  volatile int* s_warp_tiles = reinterpret_cast<volatile int*>(ctrl + 16 * Cfg::STAGES + 64);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -325,7 +329,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
     mbar_init(bar_drain, 1);
     *s_abort = 0;
     *s_bcast = 0;
-    *s_warps_done = 0;
+    for (int w = 0; w < Cfg::EPI_WARPS; ++w) s_warp_tiles[w] = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -398,8 +402,24 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
       if (*s_abort) {
-        // Let this CTA's loads in flight land before shared memory goes away.
-        for (int i = 0; i < 64; ++i) __nanosleep(4000);
+        // Loads in flight must land before shared memory goes away.  The full barrier of a stage completes
+        // when the bytes armed on it have arrived, so the leader (and the single CTA) waits, with its own
+        // short limit, on the barriers of the last STAGES iterations it issued: no later arming can follow.
+        // In a pair the barriers live in the leader and count both CTAs' bytes; the second CTA cannot wait on
+        // them (mbarrier waits are CTA-local), so it pauses for a bounded time instead, and the cluster
+        // barrier of the tear-down holds it until the leader has passed its own drain.
+        if (cta_rank == 0) {
+          const unsigned long long d2 = globaltimer_ns() + 2000000ull;
+          for (int j = it > Cfg::STAGES ? it - Cfg::STAGES : 0; j < it; ++j) {
+            const uint32_t bar = bar_full + 8 * (j % Cfg::STAGES);
+            const uint32_t ph = (j / Cfg::STAGES) & 1;
+            for (int spin = 0; spin < (1 << 20); ++spin) {
+              if (mbar_try_wait(bar, ph) || globaltimer_ns() > d2) break;
+            }
+          }
+        } else {
+          for (int i = 0; i < 64; ++i) __nanosleep(4000);
+        }
       }
     }
   } else if (warp == 1) {
@@ -608,6 +628,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           continue;
         }
         __syncwarp();
+        // Test knob: the last epilogue warp falls behind by several microseconds per tile, after it has
+        // handed the accumulator back, so the other three run ahead of it by a tile or two.
+        if ((p.ablate & 8) && ew == Cfg::EPI_WARPS - 1 && c == Cfg::BN / Cfg::EPI_CHUNK_COLS - 1) __nanosleep(8000);
         if (p.epi_st256) {
           // 8 lanes cover one row's 256 contiguous bytes with 32-byte stores; 4 rows per store instruction.
           // A lane reads its two 16-byte slots in an order that keeps each quarter-warp on 8 different banks.
@@ -658,7 +681,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         __syncwarp();
         if (lane == 0) {
           __threadfence_block();
-          atomicAdd(s_warps_done, 1);
+          s_warp_tiles[ew] = lt + 1;
         }
       }
     }
@@ -837,7 +860,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int t = group_id;
       unsigned spins = 0;
       while (t < num_tiles) {
-        const int done = *reinterpret_cast<volatile int*>(s_warps_done) / Cfg::EPI_WARPS;
+        // A tile is finished when every epilogue warp has stored its 32 rows of it.  The warps are not in
+        // lock step (a warp may be a tile or two ahead of the slowest one), so the count is the minimum of
+        // the per-warp counters, never their sum.
+        int done = s_warp_tiles[0];
+#pragma unroll
+        for (int w = 1; w < Cfg::EPI_WARPS; ++w) done = min(done, s_warp_tiles[w]);
         if (done > signalled) {
           fence_sys();
           for (; signalled < done && t < num_tiles; ++signalled, t += num_groups) {

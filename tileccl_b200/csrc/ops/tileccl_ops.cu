@@ -21,6 +21,8 @@ struct GemmPlan {
   OutMaps omaps;     // encoded only for the TMA-store epilogue
   int cta_group;
   int grid;
+  int lda, ldb;      // operand row pitches (elements), kept for tcl_gemm_plan_set_operands
+  const void* a_ptr;
 };
 
 void set_err(char* err, int errlen, const char* msg) {
@@ -29,18 +31,16 @@ void set_err(char* err, int errlen, const char* msg) {
   }
 }
 
+// Opt-in to the kernel's dynamic shared memory on the current device.  Called when a plan is created (plans
+// are per device), so that a launch touches no host state shared between threads.
 template <int G>
-cudaError_t launch_gemm(const GemmPlan* pl, cudaStream_t stream) {
+cudaError_t prepare_gemm() {
+  return cudaFuncSetAttribute(gemm_sm100_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<G>::SMEM_BYTES);
+}
+
+template <int G>
+cudaError_t launch_gemm(const GemmPlan* pl, const GemmParams& params, cudaStream_t stream) {
   using Cfg = GemmCfg<G>;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<G>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    attr_set[dev] = true;
-  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(pl->grid), 1, 1);
   cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
@@ -53,7 +53,7 @@ cudaError_t launch_gemm(const GemmPlan* pl, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<G>, pl->tmap_a, pl->tmap_b, pl->params, pl->omaps);
+  return cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<G>, pl->tmap_a, pl->tmap_b, params, pl->omaps);
 }
 
 // ---------------------------------------------------------------------------
@@ -379,6 +379,10 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
   if (grid < G) return fail("grid too small");
   pl->grid = grid;
   pl->cta_group = G;
+  pl->lda = d->lda;
+  pl->ldb = d->ldb;
+  pl->a_ptr = d->A;
+  if ((G == 2 ? prepare_gemm<2>() : prepare_gemm<1>()) != cudaSuccess) return fail("cudaFuncSetAttribute (dynamic shared memory) failed");
 
   const int box_b = 256 / G;
   int r = ptx::encode_tmap_bf16_k64(&pl->tmap_a, d->A, static_cast<uint64_t>(d->M),
@@ -394,10 +398,29 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
 int tcl_gemm_plan_run(void* plan, int epoch, void* stream) {
   GemmPlan* pl = static_cast<GemmPlan*>(plan);
   if (!pl) return static_cast<int>(cudaErrorInvalidValue);
-  pl->params.epoch = epoch;
+  // The call number travels in a copy of the parameters: a launch does not write to the plan.
+  GemmParams params = pl->params;
+  params.epoch = epoch;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = pl->cta_group == 2 ? launch_gemm<2>(pl, st) : launch_gemm<1>(pl, st);
+  cudaError_t e = pl->cta_group == 2 ? launch_gemm<2>(pl, params, st) : launch_gemm<1>(pl, params, st);
   return static_cast<int>(e);
+}
+
+int tcl_gemm_plan_set_operands(void* plan, const void* A, const void* B) {
+  GemmPlan* pl = static_cast<GemmPlan*>(plan);
+  if (!pl || !A || !B) return static_cast<int>(cudaErrorInvalidValue);
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return static_cast<int>(cudaErrorMisalignedAddress);
+  if (pl->params.mode == kModeAgGemm && A != pl->a_ptr) return static_cast<int>(cudaErrorInvalidValue);  // A is the gathered buffer the plan was built on
+  CUtensorMap ta, tb;
+  if (ptx::encode_tmap_bf16_k64(&ta, A, static_cast<uint64_t>(pl->params.M), static_cast<uint64_t>(pl->params.K),
+                                static_cast<uint64_t>(pl->lda), 128) != 0 ||
+      ptx::encode_tmap_bf16_k64(&tb, B, static_cast<uint64_t>(pl->params.N), static_cast<uint64_t>(pl->params.K),
+                                static_cast<uint64_t>(pl->ldb), static_cast<uint32_t>(256 / pl->cta_group)) != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  pl->tmap_a = ta;
+  pl->tmap_b = tb;
+  pl->a_ptr = A;
+  return 0;
 }
 
 void tcl_gemm_plan_destroy(void* plan) { delete static_cast<GemmPlan*>(plan); }

@@ -75,10 +75,18 @@ typedef struct tcl_gemm_desc {
 int tcl_gemm_desc_size(void);
 int tcl_gemm_desc_offset(const char* field);
 
-/* Returns NULL and fills err on invalid arguments. */
+/* Returns NULL and fills err on invalid arguments.  A plan belongs to the device that is current when it is
+ * created (tensor maps, shared-memory opt-in); create and run it with that device current. */
 void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen);
-/* Launches one call; epoch is the 1-based call number shared by all ranks. */
+/* Launches one call; epoch is the 1-based call number shared by all ranks.  A launch reads the plan and writes
+ * nothing to it, so several host threads may launch one plan.  The fused modes, however, own flag counters and
+ * staging buffers that one call uses at a time: calls of one fused plan must not overlap on the GPU (issue them
+ * on one stream, or order the streams with events), and every rank must make the same sequence of calls. */
 int tcl_gemm_plan_run(void* plan, int epoch, void* stream);
+/* Points the plan at other A / B operands of the same shape, pitch and alignment (re-encodes the two tensor
+ * maps on the host; no device work).  Takes effect for launches made after it returns; not safe while another
+ * thread launches the same plan.  For TCL_MODE_AG_GEMM, A is the gathered buffer and must stay what it was. */
+int tcl_gemm_plan_set_operands(void* plan, const void* A, const void* B);
 void tcl_gemm_plan_destroy(void* plan);
 int tcl_gemm_plan_grid(void* plan);
 int tcl_gemm_smem_bytes(int cta_group);

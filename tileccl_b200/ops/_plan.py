@@ -61,6 +61,15 @@ class Plan:
         _native.check(rc, "kernel launch")
         self.launches += 1
 
+    def set_operands(self, A: torch.Tensor, Bt: torch.Tensor) -> None:
+        """Points the plan at other operands of the same shape and row pitch (host-side re-encoding of the
+        two tensor maps, no device work).  The plan keeps no reference to them: the caller keeps them alive
+        until the launches that read them have finished."""
+        d = self.desc
+        if tuple(A.shape) != (d.M, d.K) or A.stride(0) != d.lda or tuple(Bt.shape) != (d.N, d.K) or Bt.stride(0) != d.ldb:
+            raise ValueError("set_operands: shape or row pitch differs from the plan's")
+        _native.check(self.lib.tcl_gemm_plan_set_operands(self.handle, C.c_void_p(A.data_ptr()), C.c_void_p(Bt.data_ptr())), "set_operands")
+
     def check(self) -> None:
         """Synchronises and raises :class:`KernelTimeout` if a wait ran out."""
         st = self.status.tolist()

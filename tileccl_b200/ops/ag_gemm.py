@@ -21,6 +21,7 @@ from __future__ import annotations
 import torch
 
 from .. import _native
+from ..parallel import group as G
 from ..parallel.heap import SymmetricHeap
 from ._plan import Plan, require_bf16_rowmajor
 
@@ -29,7 +30,7 @@ class AgGemm:
     def __init__(self, heap: SymmetricHeap, M: int, K: int, Bt: torch.Tensor, cta_group: int = 2,
                  gather_rows: int = 512, out: torch.Tensor | None = None, group_m: int = 0,
                  num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "pull", item_rows: int = 1, epi: str | None = None,
-                 device_epoch: bool = False):
+                 device_epoch: bool = False, hold_operands: bool = True):
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
         world, rank = heap.world, heap.rank
@@ -88,8 +89,14 @@ class AgGemm:
         d.timeout_ns = int(timeout_ms * 1e6)
         d.group_m, d.num_ctas = group_m, num_ctas
         d.ablate = ablate
-        self.plan = Plan(d, keep_alive=(Bt, out, self.a_full, self.flags, self.done, self.barrier), device_epoch=device_epoch)
+        own = (out, self.a_full, self.flags, self.done, self.barrier)
+        self.plan = Plan(d, keep_alive=((Bt,) + own) if hold_operands else own, device_epoch=device_epoch)
         self.gather_rows = gather_rows
+        # Construction is collective.  It ends with a host barrier behind a device synchronise: the counters
+        # zeroed above are zero on every rank before any rank's first launch can signal them.
+        if world > 1:
+            torch.cuda.synchronize()
+            G.host_barrier(heap.group)
 
     def __call__(self, stream=None) -> torch.Tensor:
         self.plan.run(stream)

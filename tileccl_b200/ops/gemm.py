@@ -16,7 +16,7 @@ class GemmPlan(Plan):
     def __init__(self, A: torch.Tensor, Bt: torch.Tensor, out: torch.Tensor | None = None,
                  cta_group: int = 2, group_m: int = 0, num_ctas: int = 0, timeout_ms: float = 4000.0,
                  dst_ptrs: list[int] | None = None, seg_rows: int | None = None, epi: str | None = None,
-                 store: str = "st16"):
+                 store: str = "st16", hold_operands: bool = True):
         """``dst_ptrs``/``seg_rows`` route row segments of D to other addresses
         (a peer's buffer): the epilogue-remote experiment.  ``store`` picks how the epilogue leaves the
         SM: ``st16`` (16-byte st.global, the default), ``st256`` (32-byte st.global.v8.b32) or ``tma``
@@ -55,7 +55,8 @@ class GemmPlan(Plan):
         d.epi_silu_mul = 1 if epi == "silu_mul" else 0
         d.epi_st256 = 1 if store == "st256" else 0
         d.epi_tma_store = 1 if store == "tma" else 0
-        super().__init__(d, keep_alive=(A, Bt, out))
+        # hold_operands=False: the caller re-points the plan with set_operands() and owns the operands' lifetime
+        super().__init__(d, keep_alive=(A, Bt, out) if hold_operands else (out,))
         self.out = out
 
     def __call__(self, stream=None) -> torch.Tensor:

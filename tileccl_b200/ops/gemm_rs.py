@@ -14,6 +14,7 @@ from __future__ import annotations
 import torch
 
 from .. import _native
+from ..parallel import group as G
 from ..parallel.heap import SymmetricHeap
 from ._plan import Plan, require_bf16_rowmajor
 
@@ -28,7 +29,7 @@ class GemmRs:
     def __init__(self, heap: SymmetricHeap, A: torch.Tensor, Bt: torch.Tensor, cta_group: int = 2,
                  rs_chunks: int = 0, comm_enabled: bool = True, group_m: int = 0, num_ctas: int = 0,
                  timeout_ms: float = 4000.0, ablate: int = 0, force_staged: bool = False, transport: str = "p2p",
-                 st256: bool = False, device_epoch: bool = False):
+                 st256: bool = False, device_epoch: bool = False, hold_operands: bool = True):
         require_bf16_rowmajor(A, "A")
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
@@ -96,8 +97,15 @@ class GemmRs:
         d.group_m, d.num_ctas = group_m, num_ctas
         d.ablate = ablate
         d.epi_st256 = 1 if st256 else 0    # 32-byte epilogue stores (st.global.v8.b32) instead of 16-byte ones
-        self.plan = Plan(d, keep_alive=(A, Bt, self.stage, self.tile_cnt, self.barrier, self.out), device_epoch=device_epoch)
+        # hold_operands=False: the caller re-points the plan with plan.set_operands() and owns the operands' lifetime
+        own = (self.stage, self.tile_cnt, self.barrier, self.out)
+        self.plan = Plan(d, keep_alive=((A, Bt) + own) if hold_operands else own, device_epoch=device_epoch)
         self.rs_chunks = rs_chunks
+        # Construction is collective.  It ends with a host barrier behind a device synchronise: the counters
+        # zeroed above are zero on every rank before any rank's first launch can signal them.
+        if world > 1:
+            torch.cuda.synchronize()
+            G.host_barrier(heap.group)
 
     def __call__(self, stream=None) -> torch.Tensor:
         self.plan.run(stream)

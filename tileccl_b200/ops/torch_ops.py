@@ -8,10 +8,15 @@
     h       = torch.ops.tileccl.silu_mul(gate_up)
     torch.ops.tileccl.barrier()                      # device barrier over all ranks, on the current stream
 
-Plans (tensor maps, staging buffers, counters) are built on first use for a given set of operand
-addresses and shapes and are cached; results live in buffers owned by the cached plan, so a result is
-valid until the next call with the same operands.  Inputs that must be peer-visible (the AG shard) are
-copied into the plan's slot of the symmetric heap when they are not already there.
+Plans (tensor maps, staging buffers, counters) are built on first use for a given operand *layout* (shapes,
+row pitches) and are cached; the operands' addresses are not part of the key.  Every call points the cached
+plan at the tensors it was given (a host-side re-encoding of two tensor maps) and keeps no reference to them,
+so a loop that allocates fresh activations every step reuses one plan and one set of staging buffers, and
+every rank builds the same plans in the same order whatever addresses its allocator hands out.  Results live
+in buffers owned by the cached plan: a result is valid until the next call with operands of the same layout.
+Inputs that must be peer-visible (the AG shard) are copied into the plan's slot of the symmetric heap when
+they are not already there.  Building a fused plan allocates from the symmetric heap and is collective: all
+ranks must make the same sequence of first calls.
 
 The reference stops at C++ programs; this layer is what the north star adds.
 """
@@ -56,7 +61,8 @@ def symm_empty(shape, dtype=torch.bfloat16) -> torch.Tensor:
 
 
 def _key(kind, *tensors, extra=()):
-    return (kind,) + tuple((t.data_ptr(), tuple(t.shape), tuple(t.stride())) for t in tensors) + tuple(extra)
+    """Cache key: the operands' layout only (never their addresses)."""
+    return (kind,) + tuple((tuple(t.shape), tuple(t.stride()), str(t.dtype)) for t in tensors) + tuple(extra)
 
 
 def check_all() -> None:
@@ -77,7 +83,9 @@ def _gemm(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
     k = _key("gemm", a, b_t)
     plan = _ctx["plans"].get(k)
     if plan is None:
-        plan = _ctx["plans"][k] = GemmPlan(a, b_t, cta_group=_ctx["cta_group"] if a.shape[0] % 256 == 0 else 1)
+        plan = _ctx["plans"][k] = GemmPlan(a, b_t, cta_group=_ctx["cta_group"] if a.shape[0] % 256 == 0 else 1, hold_operands=False)
+    else:
+        plan.set_operands(a, b_t)
     return plan()
 
 
@@ -87,7 +95,9 @@ def _gemm_rs(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
     if op is None:
         h = heap()
         g = _ctx["cta_group"] if (a.shape[0] // h.world) % 256 == 0 else 1
-        op = _ctx["plans"][k] = GemmRs(h, a, b_t, cta_group=g)
+        op = _ctx["plans"][k] = GemmRs(h, a, b_t, cta_group=g, hold_operands=False)
+    else:
+        op.plan.set_operands(a, b_t)
     return op()
 
 
@@ -98,7 +108,9 @@ def _ag_gemm(a_shard: torch.Tensor, b_t: torch.Tensor, gather_rows: int = 512) -
     op = _ctx["plans"].get(k)
     if op is None:
         g = _ctx["cta_group"] if a_shard.shape[0] % 256 == 0 else 1
-        op = _ctx["plans"][k] = AgGemm(h, M, K, b_t, cta_group=g, gather_rows=gather_rows)
+        op = _ctx["plans"][k] = AgGemm(h, M, K, b_t, cta_group=g, gather_rows=gather_rows, hold_operands=False)
+    else:
+        op.plan.set_operands(op.a_full, b_t)
     if a_shard.data_ptr() != op.a_shard.data_ptr():
         op.a_shard.copy_(a_shard)
     return op()

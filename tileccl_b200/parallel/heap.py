@@ -17,11 +17,13 @@ and has no heap and no multicast mapping.
 """
 from __future__ import annotations
 
+import atexit
 import ctypes as C
 import math
 import os
 import socket
 import time
+import weakref
 
 import torch
 
@@ -68,7 +70,38 @@ class SymmetricHeap:
         else:
             raise ValueError(f"unknown heap back end {backend!r}")
         self._local = torch.as_tensor(_RawMem(self.base[self.rank], self.nbytes, self), device=f"cuda:{self.device}")
+        if self.mc_base is not None:
+            # A process must not end with its memory still bound to the NVLink multicast object while peers hold
+            # mappings of it: whatever ends this process (an exception on another path, sys.exit), the binding is
+            # taken down first, locally and without waiting for anybody.
+            ref = weakref.ref(self)
+            atexit.register(lambda: ref() is not None and ref().release_multicast())
         G.host_barrier(group)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        if exc_type is None:
+            self.close()
+        else:
+            # Peers may be anywhere: no collective step on the way out of a failure.
+            self.release_multicast()
+        return False
+
+    def release_multicast(self) -> None:
+        """Local, barrier-free teardown of the multicast binding and mapping (no-op without one, and the second
+        time).  For failure paths and process exit; the orderly, collective teardown is :meth:`close`.  After
+        it the heap still serves peer loads and stores, but ``mc_ptr`` addresses are gone."""
+        if self.mc_base is None:
+            return
+        try:
+            torch.cuda.synchronize()
+        except Exception:  # noqa: BLE001  (a failed context must not stop the unbind)
+            pass
+        mc, self.mc_base = self.mc_base, None
+        self.lib.tcl_mc_unbind(self._mc_handle, self.device, self.nbytes)
+        self.lib.tcl_vmm_unmap(C.c_void_p(mc), self.nbytes, self._mc_handle)
 
     # ---- back ends -------------------------------------------------------------
     def _init_ipc(self, nbytes: int) -> None:
@@ -240,10 +273,7 @@ class SymmetricHeap:
         elif self.backend == "vmm" and self.base[self.rank]:
             # Order matters: nobody may lose its memory while a peer can still reach it through the
             # multicast object or a peer mapping.  Every step is followed by a host barrier.
-            if self.mc_base is not None:
-                self.lib.tcl_mc_unbind(self._mc_handle, self.device, self.nbytes)
-                self.lib.tcl_vmm_unmap(C.c_void_p(self.mc_base), self.nbytes, self._mc_handle)
-                self.mc_base = None
+            self.release_multicast()
             G.host_barrier(self.group)
             own = self._handles[0]
             for r, h in zip([x for x in range(self.world) if x != self.rank], self._handles[1:]):

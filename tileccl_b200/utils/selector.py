@@ -37,6 +37,9 @@ class Platform:
     sms: int = 148
     # link bandwidth per direction, GB/s
     ce_gbps: float = 749.0            # copy engine, 128 MB copy
+    peer_copy_gbps: float = 770.0     # large one-direction peer copy: the link denominator of the rooflines (utils/roofline.py)
+    peer_copy_source: str = ""        # where that figure was measured
+    link_nominal_gbps: float = 900.0  # the link's nominal rate per direction, for context
     sm_gbps: float = 700.0            # register or bulk-copy mover, any message >= 2 KB
     per_sm_gbps: float = 50.0         # what one SM of a mover sustains; 16 SMs saturate the link
     fused_st_gbps: float = 620.0      # 16-byte peer stores from a GEMM epilogue (all-to-all pattern)
