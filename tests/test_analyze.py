@@ -92,17 +92,23 @@ def test_tuning_summary_sorts_knob_settings(tmp_path):
 
 
 def test_sweep_settings_match_the_op_and_the_analyser():
-    """Every setting of the sweep driver is a keyword of GemmRs, and its knobs string is what the analyser
-    recognises as the default."""
+    """Every setting of the sweep driver is a keyword of the op it tunes, and the analyser finds each sweep's
+    default row."""
     import inspect
 
-    from tileccl_b200.bench import tune_gemm_rs
+    from tileccl_b200.bench import tune_fused
+    from tileccl_b200.ops.ag_gemm import AgGemm
     from tileccl_b200.ops.gemm_rs import GemmRs
-    params = set(inspect.signature(GemmRs.__init__).parameters)
-    for name, kw in tune_gemm_rs.SETTINGS.items():
-        assert set(kw) <= params, name
-    assert tune_gemm_rs.knobs_string({}) == "cta_group=2|transport=p2p|rs_chunks=0|group_m=0|num_ctas=0|st256=0|ablate=0"
-    rows = [{"max_over_ranks_us": "800", "nccl_cublas_us": "1200", "knobs": tune_gemm_rs.knobs_string({})},
-            {"max_over_ranks_us": "760", "nccl_cublas_us": "1200", "knobs": tune_gemm_rs.knobs_string({"st256": True})}]
+    for settings, op in ((tune_fused.RS_SETTINGS, GemmRs), (tune_fused.AG_SETTINGS, AgGemm)):
+        params = set(inspect.signature(op.__init__).parameters)
+        for name, kw in settings.items():
+            assert set(kw) <= params, name
+    base = {"cta_group": 2, "transport": "p2p", "rs_chunks": 0, "group_m": 0, "num_ctas": 0, "st256": 0, "ablate": 0}
+    assert tune_fused.knobs_string({}, base) == "cta_group=2|transport=p2p|rs_chunks=0|group_m=0|num_ctas=0|st256=0|ablate=0"
+    rows = [{"max_over_ranks_us": "800", "nccl_cublas_us": "1200", "knobs": "op=gemm_rs|setting=default|" + tune_fused.knobs_string({}, base)},
+            {"max_over_ranks_us": "760", "nccl_cublas_us": "1200", "knobs": "op=gemm_rs|setting=st256|" + tune_fused.knobs_string({"st256": True}, base)},
+            {"max_over_ranks_us": "1400", "nccl_cublas_us": "2100", "knobs": "op=ag_gemm|setting=default|gather_rows=512"},
+            {"max_over_ranks_us": "1250", "nccl_cublas_us": "2100", "knobs": "op=ag_gemm|setting=nowait|ablate=4"}]
     txt = analyze.tuning_summary(rows)
     assert "1.053x of default" in txt and txt.index("st256=1") < txt.index("st256=0")
+    assert "fused ag_gemm" in txt and "1.120x of default" in txt

@@ -228,26 +228,31 @@ def interference_sanity(bundle: str) -> str:
 
 
 def tuning_summary(rows: list[dict]) -> str:
-    """Knob sweep of the fused GEMM+RS (``run_all --tuning``): one line per knob setting, fastest first."""
+    """Knob sweeps of the fused ops (``run_all --tuning``): per op, one line per knob setting, fastest first,
+    against NCCL + cuBLAS and against the default setting of the same sweep."""
     if not rows:
         return ""
-    best: dict[str, tuple[float, float]] = {}
+    by_op: dict[str, dict[str, tuple[float, float]]] = {}
     for r in rows:
         t, n = _f(r, "max_over_ranks_us"), _f(r, "nccl_cublas_us")
+        k = r.get("knobs", "?")
+        op = next((p[3:] for p in k.split("|") if p.startswith("op=")), "gemm_rs")
         if t > 0:
-            best[r.get("knobs", "?")] = (t, n)       # every rank's row carries the same max over ranks
-    if not best:
-        return ""
-    out = ["## knob sweep of the fused GEMM+RS (max over ranks)"]
-    ref = best.get(next((k for k in best if "rs_chunks=0|group_m=0|num_ctas=0|st256=0" in k and "cta_group=2" in k and "transport=p2p" in k), ""), None)
-    for k, (t, n) in sorted(best.items(), key=lambda kv: kv[1][0]):
-        rel = f"  {ref[0] / t:5.3f}x of default" if ref else ""
-        out.append(f"  {t:9.1f} us  {n / t if t else 0:5.3f}x of NCCL+cuBLAS{rel}  {k}")
-    return "\n".join(out) + "\n"
+            by_op.setdefault(op, {})[k] = (t, n)       # every rank's row carries the same max over ranks
+    out = []
+    for op, best in by_op.items():
+        out.append(f"## knob sweep of the fused {op} (max over ranks)")
+        ref = next((v for k, v in best.items() if "setting=default" in k), None)
+        if ref is None:   # rows without a setting name: the default is the row with every knob at its default
+            ref = next((v for k, v in best.items() if "rs_chunks=0|group_m=0|num_ctas=0|st256=0|ablate=0" in k and "cta_group=2" in k and "transport=p2p" in k), None)
+        for k, (t, n) in sorted(best.items(), key=lambda kv: kv[1][0]):
+            rel = f"  {ref[0] / t:5.3f}x of default" if ref else ""
+            out.append(f"  {t:9.1f} us  {n / t if t else 0:5.3f}x of NCCL+cuBLAS{rel}  {k}")
+    return "\n".join(out) + "\n" if out else ""
 
 
 def report(bundle: str) -> str:
-    parts = [f"# analysis of {bundle}\n"]
+    parts = [f"# analysis of {os.path.basename(os.path.normpath(bundle))}\n"]
     ms = read(os.path.join(bundle, "exp3_fused_msweep.csv"))
     ks = read(os.path.join(bundle, "exp3_fused_ksweep.csv"))
     parts += [msweep(ms), verdict_shift_or_tail(ms), verdict_tiles_or_duration(ks), verdict_order(read(os.path.join(bundle, "exp3_order.csv"))),

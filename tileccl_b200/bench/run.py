@@ -5,23 +5,109 @@
         tileccl_b200/bench/run.py exp3_gemm_rs_fused --m 32768 --n 8192 --k 1024 --verify
 
 The first argument names a module of ``tileccl_b200.bench``; the rest are its flags.
+
+Several experiments can share one set of rank processes (one start-up, one NCCL rendezvous): separate
+them with ``--then``, optionally naming each with ``--as NAME``.  With ``--manifest FILE`` rank 0 appends
+one line per experiment (``NAME rc=... seconds=...``, the orchestrator's manifest format) and with
+``--logs DIR`` each experiment's rank-0 output goes to ``DIR/NAME.log``.  An experiment that raises is
+recorded and the batch goes on with the next one only if every rank agrees that it is still in step.
+
+    run.py --manifest out/manifest.txt --logs out exp3_gemm_rs_fused --m 512 ... --as exp3_m512 \\
+           --then exp3_gemm_rs_fused --m 1024 ... --as exp3_m1024
 """
+import contextlib
 import importlib
 import os
 import sys
+import time
+import traceback
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 EXPERIMENTS = ("exp1_ce_interference", "exp2_ag_gemm_granularity", "exp3_epilogue_remote",
-               "exp3_gemm_rs_fused", "mlp_e2e", "nvls_bw", "gemm_vs_cublas", "once", "tune_gemm_rs")
+               "exp3_gemm_rs_fused", "mlp_e2e", "nvls_bw", "gemm_vs_cublas", "once", "tune_fused")
+
+
+def split_batch(argv: list[str]) -> tuple[dict, list[tuple[str, str, list[str]]]]:
+    """(options, [(name, module, flags), ...]) from a command line with ``--then`` separators."""
+    opts = {"manifest": None, "logs": None}
+    while argv and argv[0] in ("--manifest", "--logs"):
+        opts[argv[0][2:]] = argv[1]
+        argv = argv[2:]
+    jobs, cur = [], []
+    for a in argv + ["--then"]:
+        if a == "--then":
+            if cur:
+                name = cur[0]
+                if "--as" in cur:
+                    i = cur.index("--as")
+                    name = cur[i + 1]
+                    cur = cur[:i] + cur[i + 2:]
+                jobs.append((name, cur[0], cur[1:]))
+            cur = []
+        else:
+            cur.append(a)
+    return opts, jobs
 
 
 def main() -> int:
-    if len(sys.argv) < 2 or sys.argv[1] not in EXPERIMENTS:
-        print(f"usage: run.py <{'|'.join(EXPERIMENTS)}> [flags]", file=sys.stderr)
+    opts, jobs = split_batch(sys.argv[1:])
+    if not jobs or any(mod not in EXPERIMENTS for _, mod, _ in jobs):
+        print(f"usage: run.py [--manifest FILE] [--logs DIR] <{'|'.join(EXPERIMENTS)}> [flags] [--as NAME] [--then <experiment> [flags] ...]", file=sys.stderr)
         return 1
-    mod = importlib.import_module(f"tileccl_b200.bench.{sys.argv[1]}")
-    return int(mod.main(sys.argv[2:]) or 0)
+    if len(jobs) == 1 and not opts["manifest"] and not opts["logs"]:
+        mod = importlib.import_module(f"tileccl_b200.bench.{jobs[0][1]}")
+        return int(mod.main(jobs[0][2]) or 0)
+
+    import torch
+    from tileccl_b200.parallel import group as G
+    rank, world, _ = G.init()
+    G.hold()
+    worst = 0
+    try:
+        for name, modname, flags in jobs:
+            t0 = time.time()
+            log = open(os.path.join(opts["logs"], f"{name}.log"), "w") if (opts["logs"] and rank == 0) else None
+            rc = 0
+            try:
+                with contextlib.ExitStack() as st:
+                    if log:
+                        log.write(f"$ {modname} {' '.join(flags)}\n")
+                        log.flush()
+                        st.enter_context(contextlib.redirect_stdout(log))
+                    mod = importlib.import_module(f"tileccl_b200.bench.{modname}")
+                    rc = int(mod.main(list(flags)) or 0)
+            except SystemExit as e:
+                rc = int(e.code or 0) if isinstance(e.code, int) else 1
+            except Exception:  # noqa: BLE001  (recorded; whether the batch can go on is decided below)
+                rc = 1
+                text = traceback.format_exc()
+                (log or sys.stderr).write(text)
+                if log:
+                    sys.stderr.write(f"[{name}] {text.splitlines()[-1]}\n")
+            finally:
+                if log:
+                    log.close()
+            # every rank must have left the experiment the same way, else the ranks are out of step
+            flag = torch.tensor([rc, -rc], device="cuda")
+            if world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            rc_all, rc_min = int(flag[0]), -int(flag[1])
+            worst = max(worst, rc_all)
+            if rank == 0:
+                print(f"  {name}: rc={rc_all} in {time.time() - t0:.1f} s", flush=True)
+                if opts["manifest"]:
+                    with open(opts["manifest"], "a") as mf:
+                        mf.write(f"{name} rc={rc_all} seconds={time.time() - t0:.1f}\n")
+            if rc_all != rc_min:
+                break          # the ranks left this experiment in different ways: stop rather than run out of step
+            if rc_all != 0:
+                torch.cuda.synchronize()
+    finally:
+        G.release()
+        G.shutdown()
+    return 0 if worst == 0 else 1
 
 
 if __name__ == "__main__":

@@ -164,9 +164,9 @@ def plan(n_gpus: int, quick: bool, out: Path, tuning: bool = False) -> list[tupl
     steps.append(("exp3_fused_nvls", launch + ["exp3_gemm_rs_fused", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it, "--transport", "nvls", "--verify",
                                                 "--csv", f"{o}/exp3_fused_nvls.csv"], 600, 2))
     if tuning:
-        # knob sweep of the fused GEMM+RS at the headline shape: all settings in one process per rank, timed in turn
-        steps.append(("tune_gemm_rs", launch + ["tune_gemm_rs", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", "10" if quick else "30",
-                                                "--csv", f"{o}/exp3_tuning.csv"], 900, 2))
+        # knob sweeps of both fused ops at the headline shapes: all settings in one process per rank, timed in turn
+        steps.append(("tune_fused", launch + ["tune_fused", "--ops", "rs,ag", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", "10" if quick else "30",
+                                              "--csv", f"{o}/exp3_tuning.csv"], 900, 2))
     steps.append(("mlp_e2e", launch + ["mlp_e2e", "--iters", "10" if quick else "50", "--verify", "--csv", f"{o}/mlp_e2e.csv"], 900, 1))
     steps.append(("bench", [py, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={max(1, n_gpus)}", "--master-addr", "127.0.0.1", "--master-port", "29571",
                             "bench.py", "--gpus", str(max(1, n_gpus)), "--steps", "10" if quick else "30", "--warmup", "5"], 900, 1))
@@ -219,7 +219,7 @@ def main(argv=None) -> int:
     ap.add_argument("--force", action="store_true", help="run even if the pre-check finds the GPUs busy")
     ap.add_argument("--only", default=None, help="comma list of step-name prefixes")
     ap.add_argument("--list", action="store_true")
-    ap.add_argument("--tuning", action="store_true", help="add the knob sweep of the fused GEMM+RS (step tune_gemm_rs, CSV exp3_tuning.csv)")
+    ap.add_argument("--tuning", action="store_true", help="add the knob sweeps of the two fused ops (step tune_fused, CSV exp3_tuning.csv)")
     ap.add_argument("--keep", action="store_true", help="do not zip the bundle")
     ap.add_argument("--ncu", action="store_true", help="also capture the NVLink section of one peer_l2_probe launch with ncu (off by default; needs profiling permission)")
     args = ap.parse_args(argv)

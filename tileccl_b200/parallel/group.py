@@ -77,6 +77,21 @@ def max_over_ranks(value: float, group=None) -> float:
     return float(t.item())
 
 
+_holds = 0
+
+
+def hold() -> None:
+    """Keeps the process group alive across several experiments run in one process per rank: until the
+    matching :func:`release`, :func:`shutdown` does nothing (and :func:`init` finds the group still up)."""
+    global _holds
+    _holds += 1
+
+
+def release() -> None:
+    global _holds
+    _holds = max(0, _holds - 1)
+
+
 def shutdown() -> None:
-    if dist.is_initialized():
+    if _holds == 0 and dist.is_initialized():
         dist.destroy_process_group()
