@@ -65,6 +65,7 @@ class GemmDesc(C.Structure):
         ("ablate", C.c_int32),
         ("epi_st256", C.c_int32),
         ("epi_tma_store", C.c_int32),
+        ("ag_warps", C.c_int32),
         ("epoch_dev", C.c_void_p),
     ]
 

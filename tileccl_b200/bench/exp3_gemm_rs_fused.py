@@ -49,7 +49,7 @@ def build_parser():
     ap.add_argument("--rs-chunks", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--num-ctas", type=int, default=0, help="CTAs of the fused and ctrl variants (0 = one per SM)")
-    ap.add_argument("--ablate", type=int, default=0, help="timing-only knobs of the fused variant: 1 = no reduce warps, 2 = no tile signals, 3 = both")
+    ap.add_argument("--ablate", type=int, default=0, help="timing-only knobs of the fused variant: 1 = no reduce warps, 2 or 3 = no tile signals and no reduce warps")
     ap.add_argument("--transport", default="p2p", choices=["p2p", "nvls"], help="p2p: epilogue pushes partial tiles to the owner; nvls: partials stay local, the owner pulls sums with multimem.ld_reduce")
     ap.add_argument("--st256", action="store_true", help="fused variant: 32-byte epilogue stores (st.global.v8.b32) instead of 16-byte ones")
     ap.add_argument("--verify", action="store_true")

@@ -8,8 +8,8 @@ compare).  A device barrier and an L2 flush run, untimed, ahead of every timed c
     python -m tileccl_b200.launch -n 8 tune_fused --ops rs,ag --csv tuning.csv
 
 GEMM + reduce-scatter settings: default; 32-byte epilogue stores; raster group heights; chunks per segment;
-fewer CTAs; single-CTA tiles; the in-switch reduction (`nvls`, when the GPUs support multicast); and three
-timing-only ablations (no reduce warps, no tile signals, neither).  All-gather + GEMM settings: gather
+fewer CTAs; single-CTA tiles; the in-switch reduction (`nvls`, when the GPUs support multicast); and two
+timing-only ablations (no reduce warps; no tile signals and no reduce warps).  All-gather + GEMM settings: gather
 granularities, 8-row work items, the push form, single-CTA tiles, and two floors of the same kernel: `nowait`
 (the TMA producer does not wait for gathered rows: what the gather costs in exposed time is
 default - nowait) and `nocomm` (no gather at all).  Results of the ablations and floors are not valid
@@ -43,18 +43,19 @@ RS_SETTINGS: dict[str, dict] = {
     "ctas128": {"num_ctas": 128}, "ctas96": {"num_ctas": 96}, "ctas64": {"num_ctas": 64},
     "cg1": {"cta_group": 1},
     "nvls": {"transport": "nvls"},
-    "noreduce": {"ablate": 1}, "nosignal": {"ablate": 2}, "nocomm_warps": {"ablate": 3},
+    "noreduce": {"ablate": 1}, "nosignal": {"ablate": 3},
 }
 AG_SETTINGS: dict[str, dict] = {
     "default": {},
     "gr128": {"gather_rows": 128}, "gr2048": {"gather_rows": 2048}, "gr4096": {"gather_rows": 4096},
     "item8": {"item_rows": 8},
+    "gw2": {"gather_warps": 2}, "gw1": {"gather_warps": 1},
     "gm4": {"group_m": 4}, "gm16": {"group_m": 16},
     "cg1": {"cta_group": 1},
     "push": {"transport": "push"},
     "nowait": {"ablate": 4}, "nocomm": {"comm_enabled": False},
 }
-TIMING_ONLY = {"noreduce", "nosignal", "nocomm_warps", "nowait", "nocomm"}
+TIMING_ONLY = {"noreduce", "nosignal", "nowait", "nocomm"}
 
 
 def knobs_string(kw: dict, base: dict) -> str:

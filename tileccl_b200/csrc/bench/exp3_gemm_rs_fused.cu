@@ -5,12 +5,16 @@
 //   base  plain tcgen05 GEMM      ctrl  fused kernel, communication off      fused  the real thing
 // one iteration of each in turn, a device barrier before every timed iteration, per-iteration CUDA
 // events; fp32 verification against the sum of every rank's base result; the reference's 27 CSV
-// columns (NCCL columns stay empty here: this program links no NCCL).
+// columns (NCCL columns stay empty here: this program links no NCCL).  --order picks the variants and their
+// order inside an iteration, --dump-iters writes every rank's per-iteration times, --warmup-ms adds a
+// wall-clock warm-up whose iteration count rank 0 derives from its own pace and shares with the others
+// through the launcher's shared blob (every rank must make the same number of fused launches).
 //
 // Reference parity: comm_comp/exp3_gemm_rs_fused.cu (main :337-691) on top of
 // comm_comp/ipc_multiproc.cuh; --k is K per rank as there, --k-global shards a global K.
 #include <unistd.h>
 
+#include <chrono>
 #include <string>
 #include <vector>
 
@@ -58,7 +62,8 @@ static bool share(Launcher& L, int slot, Buf& b) {
 int main(int argc, char** argv) {
   int M = 8192, N = 8192, K = 0, k_global = 8192, ndev = 0, iters = 50, warm = 5, cta_group = 2;
   bool verify = false;
-  std::string csv_path;
+  double warmup_ms = 0;
+  std::string csv_path, order_arg = "base,ctrl,fused", dump_prefix;
   Args a(argc, argv);
   while (a.more()) {
     std::string f = a.flag(), v;
@@ -73,11 +78,24 @@ int main(int argc, char** argv) {
     else if (f == "--cta-group") cta_group = std::atoi(need().c_str());
     else if (f == "--verify") verify = true;
     else if (f == "--csv") csv_path = need();
+    else if (f == "--order") order_arg = need();
+    else if (f == "--dump-iters") dump_prefix = need();
+    else if (f == "--warmup-ms") warmup_ms = std::atof(need().c_str());
     else {
-      std::printf("usage: %s [--m M] [--n N] [--k K_per_rank | --k-global K] [--ndev W] [--iters I] [--warmup W] [--cta-group 1|2] [--verify] [--csv FILE]\n", argv[0]);
+      std::printf("usage: %s [--m M] [--n N] [--k K_per_rank | --k-global K] [--ndev W] [--iters I] [--warmup W] [--warmup-ms MS]\n"
+                  "          [--order base,ctrl,fused] [--dump-iters PREFIX] [--cta-group 1|2] [--verify] [--csv FILE]\n", argv[0]);
       return f == "-h" || f == "--help" ? 0 : 1;
     }
   }
+  static const char* kVariantNames[3] = {"base", "ctrl", "fused"};
+  std::vector<int> order;
+  for (auto& name : split_csv(order_arg)) {
+    int id = -1;
+    for (int v = 0; v < 3; ++v) if (name == kVariantNames[v]) id = v;
+    if (id < 0) { std::fprintf(stderr, "--order: unknown variant %s (base, ctrl, fused)\n", name.c_str()); return 1; }
+    order.push_back(id);
+  }
+  if (order.empty()) { std::fprintf(stderr, "--order is empty\n"); return 1; }
   const int have = Launcher::probe_device_count();     // in a child: this process stays CUDA-free until after fork
   const int world = ndev > 0 ? ndev : have;
   if (world < 1 || world > have || world > TCL_MAX_WORLD) { std::fprintf(stderr, "need %d GPUs, have %d\n", world, have); return 1; }
@@ -154,17 +172,39 @@ int main(int argc, char** argv) {
   TCL_CUDA_CHECK(cudaEventCreate(&e1));
   std::vector<double> us[3];
   if (!L.barrier()) die("a rank failed before timing");
-  for (int it = 0; it < warm + iters; ++it) {
+  auto one_iteration = [&](bool record) {
     if (L.failed()) die("a peer failed during timing");   // learnt on the host, before the next launch
-    for (int v = 0; v < 3; ++v) {
+    for (int v : order) {
       tcl_barrier_all(bar_ptrs, world, rank, ++bar_epoch, status + 8, 0, st);
       TCL_CUDA_CHECK(cudaEventRecord(e0, st));
       if (tcl_gemm_plan_run(plans[v], ++epochs[v], st) != 0) die("launch failed");
       TCL_CUDA_CHECK(cudaEventRecord(e1, st));
       TCL_CUDA_CHECK(cudaEventSynchronize(e1));
-      if (it >= warm) us[v].push_back(elapsed_us(e0, e1));
+      if (record) us[v].push_back(elapsed_us(e0, e1));
     }
     L.beat();
+  };
+  const auto w0 = std::chrono::steady_clock::now();
+  for (int it = 0; it < warm; ++it) one_iteration(false);
+  if (warmup_ms > 0) {
+    // Rank 0 turns the wall-clock budget into an iteration count from its own pace; all ranks run that many.
+    const double spent_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - w0).count();
+    if (rank == 0) {
+      const double per_iter = warm > 0 ? spent_ms / warm : 1.0;
+      const double extra = (warmup_ms - spent_ms) / (per_iter > 1e-3 ? per_iter : 1e-3);
+      L.shm()->results[0][15] = extra > 0 ? std::ceil(std::min(extra, 1e6)) : 0.0;
+    }
+    if (!L.barrier()) die("a rank failed during warm-up");
+    const int extra_iters = static_cast<int>(L.shm()->results[0][15]);
+    for (int it = 0; it < extra_iters; ++it) one_iteration(false);
+    if (rank == 0) std::printf("# warm-up: %d + %d iterations (%.0f ms asked)\n", warm, extra_iters, warmup_ms);
+  }
+  for (int it = 0; it < iters; ++it) one_iteration(true);
+  if (!dump_prefix.empty()) {
+    Csv dump;
+    if (dump.open(dump_prefix + ".rank" + std::to_string(rank) + ".csv", "m,n,k,world,rank,variant,iter,us"))
+      for (int v : order)
+        for (size_t i = 0; i < us[v].size(); ++i) dump.row("%d,%d,%d,%d,%d,%s,%zu,%.3f", M, N, K, world, rank, kVariantNames[v], i, us[v][i]);
   }
   int hst[16];
   TCL_CUDA_CHECK(cudaMemcpy(hst, status, 64, cudaMemcpyDeviceToHost));
@@ -206,18 +246,23 @@ int main(int argc, char** argv) {
                        "base_p50,ctrl_p50,fused_p50,base_min,ctrl_min,fused_min,comm_sd_p50,comm_sd_skew,comm_abs_us,order,iters,"
                        "max_over_ranks_us,nccl_cublas_us,speedup,roofline_us,pct_roofline,dtype");
     double ctrl_max = 0, fused_max = 0;
+    auto ratio = [](double x, double y) { return y > 0 ? x / y : 0.0; };   // a variant left out of --order has no time
+    std::string order_col;
+    for (int v : order) order_col += (order_col.empty() ? "" : "|") + std::string(kVariantNames[v]);
     for (int r = 0; r < world; ++r) { ctrl_max = std::max(ctrl_max, L.shm()->results[r][4]); fused_max = std::max(fused_max, L.shm()->results[r][8]); }
     for (int r = 0; r < world; ++r) {
       const double* q = L.shm()->results[r];
       const double b = q[0], c = q[4], f = q[8];
-      const double gb = double(world - 1) / world * M * N * 2 / (f * 1e-6) / 1e9;
+      const double gb = f > 0 ? double(world - 1) / world * M * N * 2 / (f * 1e-6) / 1e9 : 0.0;
       const double rel = q[12] < 0 ? -1 : q[12] / scale;     // error on the scale of the partial sums
       char ver[48];
       if (q[12] < 0) std::snprintf(ver, sizeof(ver), "-");
       else { std::snprintf(ver, sizeof(ver), "%s (max|d|/sqrt(K*w) %.3g)", rel <= 0.05 ? "ok" : "FAIL", rel); if (rel > 0.05) rc = 4; }
-      std::printf("%4d | %9.1f %6.0f | %8.1f | %8.1f %6.0f | %6.3f %6.3f %6.3f | %9.1f | %s\n", r, b, flop / b / 1e6, c, f, flop / f / 1e6, c / b, f / c, f / b, gb, ver);
-      csv.row("%d,%d,%d,%d,%d,%.2f,%.2f,%.2f,%.2f,%.2f,%.2f,%.4f,%.4f,%.4f,%.2f,%.4g,%.2f,%.2f,%.2f,%.2f,%.2f,%.2f,%.4f,%.4f,%.2f,base|ctrl|fused,%d,%.2f,,,,,bf16", M, N, K, world, r, b,
-              q[1], c, q[5], f, q[9], c / b, f / c, f / b, gb, rel, q[2], q[6], q[10], q[3], q[7], q[11], q[10] / q[6], f / ctrl_max, f - c, iters, fused_max);
+      std::printf("%4d | %9.1f %6.0f | %8.1f | %8.1f %6.0f | %6.3f %6.3f %6.3f | %9.1f | %s\n", r, b, ratio(flop, b) / 1e6, c, f, ratio(flop, f) / 1e6, ratio(c, b), ratio(f, c),
+                  ratio(f, b), gb, ver);
+      csv.row("%d,%d,%d,%d,%d,%.2f,%.2f,%.2f,%.2f,%.2f,%.2f,%.4f,%.4f,%.4f,%.2f,%.4g,%.2f,%.2f,%.2f,%.2f,%.2f,%.2f,%.4f,%.4f,%.2f,%s,%d,%.2f,,,,,bf16", M, N, K, world, r, b,
+              q[1], c, q[5], f, q[9], ratio(c, b), ratio(f, c), ratio(f, b), gb, rel, q[2], q[6], q[10], q[3], q[7], q[11], ratio(q[10], q[6]), ratio(f, ctrl_max), f - c,
+              order_col.c_str(), iters, fused_max);
     }
     std::printf("max over ranks: fused %.1f us\n", fused_max);
   }

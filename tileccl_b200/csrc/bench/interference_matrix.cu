@@ -4,8 +4,11 @@
 //   S_m = mover bandwidth alone / mover bandwidth under the probe (communication slow-down)
 // Probes: tcgen05, mma (legacy mma.sync), ffma, hbm, l2, smem.  Movers: ce, tma (bulk copies), reg.
 // The probe runs on --probe-dev (the source or the destination GPU of the transfer) on all SMs but
-// --comm-sms, which are left to the mover.  --mode starve fills every SM with a squatter kernel and
-// shows what each mover does when it gets no SM (bounded by a deadline).
+// --comm-sms, which are left to the mover (--probe-sms sets the probe's CTA count directly).  --hbm-buf sizes
+// the hbm probe's buffer.  The mover's bandwidth alone is measured once per mover and reused for every probe
+// unless --no-alone-cache asks for a fresh figure beside each pair.  --mode starve fills every SM with a
+// squatter kernel and shows what each mover does when it gets no SM (the squatter leaves after --starve-ms,
+// one second by default, at the latest).
 //
 // Reference parity: tests/interference_matrix.cu (movers :174-254, probes :282-377, probe context
 // :558-670, matrix :846-946, starve :950-1029, CSV header :839-841).
@@ -143,6 +146,7 @@ struct Mover {
   int src, dst, blocks;
   char *s, *d;
   size_t total, msg;
+  int reg_threads = 1024, stages = 4;
   int* err;
   cudaStream_t st;
   cudaEvent_t e0, e1;
@@ -152,9 +156,9 @@ struct Mover {
       for (size_t off = 0; off < total; off += chunk)
         TCL_CUDA_CHECK(cudaMemcpyPeerAsync(d + off, dst, s + off, src, std::min(chunk, total - off), st));
     } else if (m == "reg") {
-      reg_copy_kernel<<<blocks, 1024, 0, st>>>(reinterpret_cast<const uint4*>(s), reinterpret_cast<uint4*>(d), total / msg, msg / 16);
+      reg_copy_kernel<<<blocks, reg_threads, 0, st>>>(reinterpret_cast<const uint4*>(s), reinterpret_cast<uint4*>(d), total / msg, msg / 16);
     } else {
-      TCL_CUDA_CHECK(launch_bulk_pipe(4, blocks, st, s, d, total, static_cast<uint32_t>(std::min<size_t>(msg, 32768)), kBulkCopy, err, 3000000000ull));
+      TCL_CUDA_CHECK(launch_bulk_pipe(stages, blocks, st, s, d, total, static_cast<uint32_t>(std::min<size_t>(msg, 32768)), kBulkCopy, err, 3000000000ull));
     }
   }
   // GB/s over `iters` back-to-back transfers.
@@ -173,7 +177,9 @@ struct Mover {
 int main(int argc, char** argv) {
   std::string mode = "matrix", probe_dev = "src", csv_path;
   std::vector<std::string> probes = {"tcgen05", "mma", "ffma", "hbm", "l2", "smem"}, comms = {"ce", "tma", "reg"};
-  int src = 0, dst = 1, comm_sms = 16, iters = 20, window_ms = 200;
+  int src = 0, dst = 1, comm_sms = 16, probe_sms = 0, iters = 20, window_ms = 200, reg_threads = 1024, stages = 4;
+  double starve_ms = 1000.0;
+  bool alone_cache = true;
   size_t total = size_t(256) << 20, msg = 16384, hbm_bytes = size_t(256) << 20;
   Args a(argc, argv);
   while (a.more()) {
@@ -181,7 +187,13 @@ int main(int argc, char** argv) {
     auto need = [&]() { if (!a.value(&v)) std::exit(1); return v; };
     if (f == "--mode") mode = need();
     else if (f == "--probes") probes = split_csv(need());
-    else if (f == "--comm") comms = split_csv(need());
+    else if (f == "--comm" || f == "--comms") comms = split_csv(need());
+    else if (f == "--probe-sms") probe_sms = std::atoi(need().c_str());
+    else if (f == "--hbm-buf") parse_bytes(need(), &hbm_bytes);
+    else if (f == "--starve-ms") starve_ms = std::atof(need().c_str());
+    else if (f == "--no-alone-cache") alone_cache = false;
+    else if (f == "--reg-threads") reg_threads = std::atoi(need().c_str());
+    else if (f == "--stages") stages = std::atoi(need().c_str());
     else if (f == "--probe-dev") probe_dev = need();
     else if (f == "--comm-sms") comm_sms = std::atoi(need().c_str());
     else if (f == "--msg") parse_bytes(need(), &msg);
@@ -192,17 +204,22 @@ int main(int argc, char** argv) {
     else if (f == "--dst") dst = std::atoi(need().c_str());
     else if (f == "--csv") csv_path = need();
     else {
-      std::printf("usage: %s [--mode matrix|starve] [--probes LIST] [--comm ce,tma,reg] [--probe-dev src|dst] [--comm-sms N]\n"
-                  "          [--msg B] [--total B] [--iters N] [--window-ms N] [--src N] [--dst N] [--csv FILE]\n", argv[0]);
+      std::printf("usage: %s [--mode matrix|starve] [--probes LIST] [--comms ce,tma,reg] [--probe-dev src|dst] [--comm-sms N] [--probe-sms N]\n"
+                  "          [--msg B] [--total B] [--hbm-buf B] [--iters N] [--window-ms N] [--starve-ms MS] [--no-alone-cache] [--reg-threads N]\n"
+                  "          [--stages 3|4|6|8] [--src N] [--dst N] [--csv FILE]\n", argv[0]);
       return f == "-h" || f == "--help" ? 0 : 1;
     }
   }
+  if (reg_threads < 32 || reg_threads > 1024 || reg_threads % 32) { std::fprintf(stderr, "--reg-threads must be a multiple of 32 in [32, 1024]\n"); return 1; }
+  if (stages != 3 && stages != 4 && stages != 6 && stages != 8) { std::fprintf(stderr, "--stages must be 3, 4, 6 or 8\n"); return 1; }
+  if (starve_ms <= 0 || starve_ms > 5000) { std::fprintf(stderr, "--starve-ms must lie in (0, 5000]\n"); return 1; }
+  if (hbm_bytes < (size_t(1) << 20)) { std::fprintf(stderr, "--hbm-buf must be at least 1 MiB\n"); return 1; }
   const int ndev = device_count();
   if (src >= ndev || dst >= ndev) { std::fprintf(stderr, "need GPUs %d and %d, have %d\n", src, dst, ndev); return 1; }
   if (src != dst && !enable_peer_all(std::max(src, dst) + 1)) return 1;
   total = total / msg * msg;
   Mover mv;
-  mv.src = src; mv.dst = dst; mv.total = total; mv.msg = msg; mv.blocks = comm_sms;
+  mv.src = src; mv.dst = dst; mv.total = total; mv.msg = msg; mv.blocks = comm_sms; mv.reg_threads = reg_threads; mv.stages = stages;
   TCL_CUDA_CHECK(cudaSetDevice(dst));
   TCL_CUDA_CHECK(cudaMalloc(&mv.d, total));
   TCL_CUDA_CHECK(cudaSetDevice(src));
@@ -229,11 +246,11 @@ int main(int argc, char** argv) {
     int per_sm = 0;
     TCL_CUDA_CHECK(cudaSetDevice(pdev));
     TCL_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, probe_ffma_kernel, 256, 0));
-    std::printf("# starve: %d squatter CTAs on GPU %d, deadline 1 s\n%-6s %14s %14s\n", per_sm * pc.sms, pdev, "mover", "alone_us", "starved_us");
+    std::printf("# starve: %d squatter CTAs on GPU %d, deadline %.0f ms\n%-6s %14s %14s\n", per_sm * pc.sms, pdev, starve_ms, "mover", "alone_us", "starved_us");
     for (auto& m : comms) {
       const double alone = static_cast<double>(total) / mv.gbps(m, 3) / 1e3;
       pc.pin_smem = 0;
-      pc.launch(kProbeFfma, std::min(1024, per_sm * pc.sms), 1000.0, l2);
+      pc.launch(kProbeFfma, std::min(1024, per_sm * pc.sms), starve_ms, l2);
       pc.rate(kProbeFfma, 20);
       TCL_CUDA_CHECK(cudaSetDevice(src));
       TCL_CUDA_CHECK(cudaEventRecord(mv.e0, mv.st));
@@ -248,7 +265,8 @@ int main(int argc, char** argv) {
     return 0;
   }
 
-  const int probe_blocks = pc.sms - (pdev == src ? comm_sms : 0);
+  const int probe_blocks = probe_sms > 0 ? std::min(probe_sms, pc.sms) : pc.sms - (pdev == src ? comm_sms : 0);
+  std::vector<double> alone_cached(comms.size(), -1.0);
   std::printf("# interference matrix: probe on %s GPU (%d CTAs), mover on %d SMs of GPU %d, msg %zu B, window %d ms\n", probe_dev.c_str(), probe_blocks,
               comm_sms, src, msg, window_ms);
   std::printf("%-8s %-5s | %12s %12s %6s | %12s %12s %-8s %6s\n", "probe", "comm", "comm_alone", "comm_ovl", "S_m", "probe_alone", "probe_ovl", "unit", "S_c");
@@ -260,8 +278,10 @@ int main(int argc, char** argv) {
     const double alone = pc.rate(k, window_ms);
     pc.stop();
     if (alone <= 0) { std::printf("%-8s [!] probe made NO progress\n", p.c_str()); continue; }
-    for (auto& m : comms) {
-      const double comm_alone = mv.gbps(m, iters);
+    for (size_t mi = 0; mi < comms.size(); ++mi) {
+      const std::string& m = comms[mi];
+      if (!alone_cache || alone_cached[mi] < 0) alone_cached[mi] = mv.gbps(m, iters);
+      const double comm_alone = alone_cached[mi];
       pc.launch(k, probe_blocks, 20000.0, l2);
       pc.rate(k, 30);
       // Mover and probe together: the host thread measures the probe while the mover runs.

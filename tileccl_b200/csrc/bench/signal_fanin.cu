@@ -1,6 +1,8 @@
 // signal_fanin: latency of "F producers tell one consumer they are done", push versus pull.
 //   signal      producer: st.release.sys flag                      (no payload)
-//   post        producer: plain (relaxed) flag store               (no payload)
+//   post        payload delivered and confirmed ahead of the timed window (producer: payload stores, st.release.sys
+//               on a "pre" flag, then waits for a second go); timed: second go -> st.release.sys flag.  What a
+//               signal costs when the data is already there, per payload size.
 //   push        producer: payload stores, then st.release.sys flag
 //   push_fence  producer: payload stores, __threadfence_system(), plain flag
 //   pull        consumer GPU: F CTAs load their slot from the producers' memory
@@ -34,9 +36,9 @@ __device__ __forceinline__ bool spin_ge(const int* p, int want, unsigned long lo
   }
 }
 
-// One CTA per logical producer.  go[] is local to the source GPU; sig[] and slots live on the target.
-__global__ void source_kernel(const int* go, int* sig, uint4* slots, const int* ids, size_t slot_vec, int rounds, int mode,
-                              int* err, unsigned long long timeout_ns) {
+// One CTA per logical producer.  go[] and go2[] are local to the source GPU; sig[], pre[] and slots live on the target.
+__global__ void source_kernel(const int* go, const int* go2, int* sig, int* pre, uint4* slots, const int* ids, size_t slot_vec, int rounds,
+                              int mode, int* err, unsigned long long timeout_ns) {
   const int id = ids[blockIdx.x];
   const unsigned long long deadline = globaltimer_ns() + timeout_ns;
   __shared__ int ok;
@@ -45,33 +47,45 @@ __global__ void source_kernel(const int* go, int* sig, uint4* slots, const int* 
     if (threadIdx.x == 0) ok = spin_ge(go + id, r, deadline) ? 1 : 0;
     __syncthreads();
     if (!ok) { if (threadIdx.x == 0) atomicExch(err, 1); return; }
-    if (mode == kPush || mode == kPushFence) {
+    if (mode == kPush || mode == kPushFence || mode == kPost) {
       const uint4 v = make_uint4(static_cast<unsigned>(r), static_cast<unsigned>(id), 0x5eed0000u + id, static_cast<unsigned>(r));
       for (size_t i = threadIdx.x; i < slot_vec; i += blockDim.x) st_v4(slot + i, v);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
       if (mode == kSignal || mode == kPush) st_release_sys(sig + id, r);
-      else if (mode == kPost) st_relaxed_sys(sig + id, r);
-      else { __threadfence_system(); st_relaxed_sys(sig + id, r); }
+      else if (mode == kPushFence) { __threadfence_system(); st_relaxed_sys(sig + id, r); }
+      else {
+        // post: confirm the delivery (untimed on the target), wait for the second go, then signal
+        st_release_sys(pre + id, r);
+        ok = spin_ge(go2 + id, r, deadline) ? 1 : 0;
+        if (ok) st_release_sys(sig + id, r);
+      }
     }
     __syncthreads();
+    if (!ok) { if (threadIdx.x == 0) atomicExch(err, 1); return; }
   }
 }
 
-// Target control: thread i owns producer i.  cycles[r] = clock64 window of round r.
-__global__ void target_ctrl_kernel(int* const* go_ptrs, const int* sig, int fanin, int rounds, long long* cycles, int* err,
-                                   unsigned long long timeout_ns) {
+// Target control: thread i owns producer i.  cycles[r] = clock64 window of round r.  In post mode the window
+// opens only after every producer has confirmed its payload.
+__global__ void target_ctrl_kernel(int* const* go_ptrs, int* const* go2_ptrs, const int* sig, const int* pre, int fanin, int rounds, int mode,
+                                   long long* cycles, int* err, unsigned long long timeout_ns) {
   const int i = threadIdx.x;
   const unsigned long long deadline = globaltimer_ns() + timeout_ns;
   __shared__ int bad;
   if (i == 0) bad = 0;
   __syncthreads();
   for (int r = 1; r <= rounds; ++r) {
+    if (mode == kPost && i < fanin) {
+      st_release_sys(go_ptrs[i], r);
+      if (!spin_ge(pre + i, r, deadline)) bad = 1;
+    }
     __syncthreads();
+    if (bad) { if (i == 0) atomicExch(err, 1); return; }
     const long long c0 = clock64();
     if (i < fanin) {
-      st_release_sys(go_ptrs[i], r);
+      st_release_sys(mode == kPost ? go2_ptrs[i] : go_ptrs[i], r);
       if (!spin_ge(sig + i, r, deadline)) bad = 1;
     }
     __syncthreads();
@@ -179,18 +193,21 @@ int main(int argc, char** argv) {
   // Target-side buffers: sig flags, payload slots (push destination / pull destination), cycle log.
   TCL_CUDA_CHECK(cudaSetDevice(c.target));
   print_device_line(c.target);
-  int *sig, *err_t, *counter;
+  int *sig, *pre, *err_t, *counter;
   uint4* slots_t;
   long long *cycles, *calib;
   int** go_ptrs_d;
+  int** go2_ptrs_d;
   const uint4** pull_src_d;
   TCL_CUDA_CHECK(cudaMalloc(&sig, max_f * 4));
+  TCL_CUDA_CHECK(cudaMalloc(&pre, max_f * 4));
   TCL_CUDA_CHECK(cudaMalloc(&err_t, 4));
   TCL_CUDA_CHECK(cudaMalloc(&counter, 4));
   TCL_CUDA_CHECK(cudaMalloc(&slots_t, max_f * max_size));
   TCL_CUDA_CHECK(cudaMalloc(&cycles, total_rounds * 8));
   TCL_CUDA_CHECK(cudaMalloc(&calib, 8));
   TCL_CUDA_CHECK(cudaMalloc(&go_ptrs_d, max_f * sizeof(int*)));
+  TCL_CUDA_CHECK(cudaMalloc(&go2_ptrs_d, max_f * sizeof(int*)));
   TCL_CUDA_CHECK(cudaMalloc(&pull_src_d, max_f * sizeof(uint4*)));
   cudaStream_t st_t;
   TCL_CUDA_CHECK(cudaStreamCreateWithFlags(&st_t, cudaStreamNonBlocking));
@@ -217,12 +234,13 @@ int main(int argc, char** argv) {
               c.warmup, cyc_per_us);
 
   // Source-side buffers.
-  std::vector<int*> go(nsrc), ids_d(nsrc), err_s(nsrc);
+  std::vector<int*> go(nsrc), go2(nsrc), ids_d(nsrc), err_s(nsrc);
   std::vector<uint4*> slots_s(nsrc);
   std::vector<cudaStream_t> st_s(nsrc);
   for (int g = 0; g < nsrc; ++g) {
     TCL_CUDA_CHECK(cudaSetDevice(c.sources[g]));
     TCL_CUDA_CHECK(cudaMalloc(&go[g], max_f * 4));
+    TCL_CUDA_CHECK(cudaMalloc(&go2[g], max_f * 4));
     TCL_CUDA_CHECK(cudaMalloc(&ids_d[g], max_f * 4));
     TCL_CUDA_CHECK(cudaMalloc(&err_s[g], 4));
     TCL_CUDA_CHECK(cudaMalloc(&slots_s[g], max_f * max_size));
@@ -234,29 +252,33 @@ int main(int argc, char** argv) {
 
   for (int mode : c.modes) {
     for (int F : c.fanins) {
-      std::vector<size_t> sizes = (mode == kSignal || mode == kPost) ? std::vector<size_t>{0} : c.sizes;
+      std::vector<size_t> sizes = (mode == kSignal) ? std::vector<size_t>{0} : c.sizes;
       for (size_t bytes : sizes) {
         const size_t slot_vec = bytes / 16;
         // Deal producers to source GPUs.
         std::vector<std::vector<int>> ids(nsrc);
-        std::vector<int*> go_ptrs(F);
+        std::vector<int*> go_ptrs(F), go2_ptrs(F);
         std::vector<const uint4*> pull_src(F);
         for (int i = 0; i < F; ++i) {
           const int g = i % nsrc;
           ids[g].push_back(i);
           go_ptrs[i] = go[g] + i;
+          go2_ptrs[i] = go2[g] + i;
           pull_src[i] = slots_s[g] + static_cast<size_t>(i) * slot_vec;
         }
         TCL_CUDA_CHECK(cudaSetDevice(c.target));
         TCL_CUDA_CHECK(cudaMemset(sig, 0, max_f * 4));
+        TCL_CUDA_CHECK(cudaMemset(pre, 0, max_f * 4));
         TCL_CUDA_CHECK(cudaMemset(err_t, 0, 4));
         TCL_CUDA_CHECK(cudaMemset(counter, 0, 4));
         TCL_CUDA_CHECK(cudaMemset(slots_t, 0, max_f * max_size));
         TCL_CUDA_CHECK(cudaMemcpy(go_ptrs_d, go_ptrs.data(), F * sizeof(int*), cudaMemcpyHostToDevice));
+        TCL_CUDA_CHECK(cudaMemcpy(go2_ptrs_d, go2_ptrs.data(), F * sizeof(int*), cudaMemcpyHostToDevice));
         TCL_CUDA_CHECK(cudaMemcpy(pull_src_d, pull_src.data(), F * sizeof(uint4*), cudaMemcpyHostToDevice));
         for (int g = 0; g < nsrc; ++g) {
           TCL_CUDA_CHECK(cudaSetDevice(c.sources[g]));
           TCL_CUDA_CHECK(cudaMemset(go[g], 0, max_f * 4));
+          TCL_CUDA_CHECK(cudaMemset(go2[g], 0, max_f * 4));
           TCL_CUDA_CHECK(cudaMemset(err_s[g], 0, 4));
           TCL_CUDA_CHECK(cudaMemset(slots_s[g], 0x5a, max_f * max_size));
           if (!ids[g].empty()) TCL_CUDA_CHECK(cudaMemcpy(ids_d[g], ids[g].data(), ids[g].size() * 4, cudaMemcpyHostToDevice));
@@ -284,13 +306,13 @@ int main(int argc, char** argv) {
           for (int g = 0; g < nsrc; ++g) {
             if (ids[g].empty()) continue;
             TCL_CUDA_CHECK(cudaSetDevice(c.sources[g]));
-            source_kernel<<<static_cast<unsigned>(ids[g].size()), c.threads, 0, st_s[g]>>>(go[g], sig, slots_t, ids_d[g], slot_vec, total_rounds,
-                                                                                         mode, err_s[g], 4000000000ull);
+            source_kernel<<<static_cast<unsigned>(ids[g].size()), c.threads, 0, st_s[g]>>>(go[g], go2[g], sig, pre, slots_t, ids_d[g], slot_vec,
+                                                                                         total_rounds, mode, err_s[g], 4000000000ull);
             TCL_CUDA_CHECK(cudaGetLastError());
           }
           TCL_CUDA_CHECK(cudaSetDevice(c.target));
           const int thr = std::max(64, (F + 31) / 32 * 32);
-          target_ctrl_kernel<<<1, thr, 0, st_t>>>(go_ptrs_d, sig, F, total_rounds, cycles, err_t, 4000000000ull);
+          target_ctrl_kernel<<<1, thr, 0, st_t>>>(go_ptrs_d, go2_ptrs_d, sig, pre, F, total_rounds, mode, cycles, err_t, 4000000000ull);
           TCL_CUDA_CHECK(cudaGetLastError());
         }
         if (!launched) continue;

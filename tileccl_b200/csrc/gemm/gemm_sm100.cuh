@@ -99,7 +99,7 @@ struct GemmParams {
   int epi_tma_store;  // the plain epilogue leaves through TMA: cp.async.bulk.tensor stores of 32 x 64 boxes from the
                       // warp's staging buffer (not with GEMM+RS communication, not with epi_silu_mul)
   int epi_st256;  // the plain epilogue stores 32 bytes per lane (st.global.v8.b32); needs 32-byte aligned destinations and pitch
-  int ablate;     // experiment knobs: bit 0 = no reduce warps, bit 1 = no tile signals, bit 2 = AG+GEMM producer
+  int ablate;     // experiment knobs: bit 0 = no reduce warps, bit 1 = no tile signals (and no reduce warps), bit 2 = AG+GEMM producer
                   // does not wait for gathered rows (these three: timing only, the output is not valid);
                   // bit 3 = the last epilogue warp sleeps a few microseconds before the final stores of every
                   // tile (the output stays valid: a test of the publish-after-all-stores rule)
@@ -126,6 +126,7 @@ struct GemmParams {
   int gather_rows;
   int ag_item_rows;                        // rows one gather warp moves per work item (and per counter arrival);
                                            // small items make rows land progressively, in schedule order
+  int ag_warps;                            // gather warps per CTA that take part (1..4); the others idle
   int* ag_done;                            // local: gather warps that finished (monotonic)
   int* ag_read_done[kMaxWorld];            // rank s's "peers done reading me" counter
   // Push form of the all-gather: every rank stores its own shard into every peer's gathered buffer.
@@ -691,7 +692,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ===== communication warps =====
     const int cw = warp - (2 + Cfg::EPI_WARPS);
     const int ctid = threadIdx.x - (2 + Cfg::EPI_WARPS) * 32;  // 0..127
-    if (p.mode == kModeGemmRs && p.comm_enabled && !(p.ablate & 1)) {
+    if (p.mode == kModeGemmRs && p.comm_enabled && !(p.ablate & 3)) {   // without tile signals there is nothing to wait for either
       // ---- reduce warps: sum the `world` staged partials of each tile of this
       // rank's segment, in the order in which the producers complete them ----
       const int items = (p.seg_rows / Cfg::BM) * sched.n_tiles;
@@ -742,10 +743,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // round trip, so a few warps per SM reach the link rate; items go out in row order, which is
         // the order in which every consumer's schedule needs them. ----
         const int items = p.seg_rows / p.ag_item_rows;
-        const int gw = blockIdx.x * Cfg::COMM_WARPS + cw;
-        const int n_gw = gridDim.x * Cfg::COMM_WARPS;
+        const int gw = blockIdx.x * p.ag_warps + cw;
+        const int n_gw = gridDim.x * p.ag_warps;
         const size_t item_bytes = static_cast<size_t>(p.ag_item_rows) * p.K * 2;
-        for (int j = gw; j < items; j += n_gw) {
+        for (int j = cw < p.ag_warps ? gw : items; j < items; j += n_gw) {
           const size_t grow = static_cast<size_t>(p.rank) * p.seg_rows + static_cast<size_t>(j) * p.ag_item_rows;
           const size_t boff = grow * p.K * 2;
           const char* src = reinterpret_cast<const char*>(p.ag_full) + boff;
@@ -776,10 +777,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
       } else if (good) {
         const int items_per_seg = p.seg_rows / p.ag_item_rows;
         const int total = (p.world - 1) * items_per_seg;
-        const int gw = blockIdx.x * Cfg::COMM_WARPS + cw;
-        const int n_gw = gridDim.x * Cfg::COMM_WARPS;
+        const int gw = blockIdx.x * p.ag_warps + cw;
+        const int n_gw = gridDim.x * p.ag_warps;
         const size_t item_bytes = static_cast<size_t>(p.ag_item_rows) * p.K * 2;
-        for (int j = gw; j < total; j += n_gw) {
+        for (int j = cw < p.ag_warps ? gw : total; j < total; j += n_gw) {
           const int step = j / items_per_seg + 1;
           const int i = j - (step - 1) * items_per_seg;
           const int seg = (p.rank + step) % p.world;
@@ -830,7 +831,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         // Tell the peers when this rank has read everything it needs from them:
         // the last gather warp of the grid sends one signal per peer.
-        if (lane == 0) {
+        if (lane == 0 && cw < p.ag_warps) {
           const int done = atom_add_acq_rel_gpu(p.ag_done, 1) + 1;
           if (done == detail::epoch_times(epoch, n_gw)) {
             for (int s = 0; s < p.world; ++s)

@@ -198,7 +198,7 @@ int tcl_gemm_desc_offset(const char* field) {
   TCL_OFF(mode) TCL_OFF(M) TCL_OFF(lda) TCL_OFF(A) TCL_OFF(world) TCL_OFF(seg_rows) TCL_OFF(dst_base) TCL_OFF(dst_row_off)
   TCL_OFF(rs_tile_cnt) TCL_OFF(rs_stage) TCL_OFF(rs_chunks) TCL_OFF(ag_src) TCL_OFF(ag_flags) TCL_OFF(gather_rows) TCL_OFF(ag_done)
   TCL_OFF(ag_push) TCL_OFF(ag_dst) TCL_OFF(barrier) TCL_OFF(status) TCL_OFF(timeout_ns) TCL_OFF(group_m) TCL_OFF(rs_mc_stage)
-  TCL_OFF(range_lo) TCL_OFF(epi_silu_mul) TCL_OFF(ablate) TCL_OFF(epi_st256) TCL_OFF(epi_tma_store) TCL_OFF(epoch_dev)
+  TCL_OFF(range_lo) TCL_OFF(epi_silu_mul) TCL_OFF(ablate) TCL_OFF(epi_st256) TCL_OFF(epi_tma_store) TCL_OFF(epoch_dev) TCL_OFF(ag_warps)
 #undef TCL_OFF
   return -1;
 }
@@ -360,6 +360,8 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
     p.gather_rows = d->gather_rows > 0 ? d->gather_rows : d->seg_rows;
     p.ag_done = d->ag_done;
     p.ag_item_rows = d->ag_item_rows > 0 ? d->ag_item_rows : 1;
+    p.ag_warps = d->ag_warps > 0 ? d->ag_warps : GemmCfg<1>::COMM_WARPS;
+    if (p.ag_warps > GemmCfg<1>::COMM_WARPS) return fail("AG+GEMM: ag_warps must lie in 1..4");
     if (p.gather_rows % p.ag_item_rows != 0) return fail("AG+GEMM: ag_item_rows must divide gather_rows");
   } else if (d->mode != TCL_MODE_PLAIN) {
     return fail("unknown mode");

@@ -60,11 +60,12 @@ typedef struct tcl_gemm_desc {
   uint64_t range_hi[TCL_MAX_WORLD];
   int32_t epi_silu_mul; /* plain / AG+GEMM: every 256-column tile holds 128 gate columns then the 128 up columns of the same
                            features; the epilogue writes silu(gate) * up: D is [M, N/2] (ldc is its pitch) */
-  int32_t ablate;       /* experiments only: bit 0 = no reduce warps, bit 1 = no tile signals */
+  int32_t ablate;       /* experiments only: bit 0 = no reduce warps, bit 1 = no tile signals (nor reduce warps), bit 2 = AG+GEMM producer does not wait, bit 3 = one epilogue warp lags (output stays valid) */
   int32_t epi_st256;    /* the epilogue stores 32 bytes per lane (st.global.v8.b32) instead of 16; every dst_base must be
                            32-byte aligned and ldc a multiple of 16 elements; not with epi_silu_mul */
   int32_t epi_tma_store; /* the epilogue leaves through TMA (cp.async.bulk.tensor stores from the staging buffer) instead of
                             st.global; plain and AG+GEMM modes and the non-communicating GEMM+RS; not with epi_silu_mul */
+  int32_t ag_warps;      /* AG+GEMM: gather warps per CTA that take part, 1..4; 0 = all four */
   int32_t* epoch_dev;    /* optional: two zeroed ints in device memory.  When set, the kernel takes the call number from
                             epoch_dev[0] + 1 (and advances it when the call ends) instead of the `epoch` argument of
                             tcl_gemm_plan_run, so that a captured CUDA graph can replay the launch */

@@ -30,7 +30,7 @@ class AgGemm:
     def __init__(self, heap: SymmetricHeap, M: int, K: int, Bt: torch.Tensor, cta_group: int = 2,
                  gather_rows: int = 512, out: torch.Tensor | None = None, group_m: int = 0,
                  num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "pull", item_rows: int = 1, epi: str | None = None,
-                 device_epoch: bool = False, hold_operands: bool = True):
+                 device_epoch: bool = False, hold_operands: bool = True, gather_warps: int = 0):
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
         world, rank = heap.world, heap.rank
@@ -84,6 +84,7 @@ class AgGemm:
             d.range_hi[s] = heap.base[s] + heap.nbytes
         d.gather_rows = gather_rows
         d.ag_item_rows = item_rows
+        d.ag_warps = gather_warps          # gather warps per CTA that take part (0 = all four)
         self.item_rows = item_rows
         d.ag_done = self.done.data_ptr()
         d.timeout_ns = int(timeout_ms * 1e6)
