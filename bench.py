@@ -201,7 +201,9 @@ def main():
         ev = {n: [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in variants[n]]
                   for _ in range(n_steps)] for n in names}
         for i in range(n_steps):
-            for n in names:
+            # the two paths take turns at going first, so that neither always starts right after the other's
+            # last (power-hungry) kernel
+            for n in (names if i % 2 == 0 else names[::-1]):
                 for j, f in enumerate(variants[n]):
                     before_op()
                     ev[n][i][j][0].record()
@@ -334,7 +336,7 @@ def main():
                        "ag_gemm": {"M": M, "K": K_ag, "N_global": args.n_ag, "N_per_rank": N_ag, "gather_rows": args.gather_rows},
                        "global_batch": M, "seq_len": None, "parallelism": f"tp{tp}", "cta_group": args.cta_group,
                        "l2": "flushed ahead of every timed operation (256 MiB write); inputs also exceed L2",
-                       "timing": ("fused and NCCL+cuBLAS steps alternate inside one timed loop; a step is the sum of its two operations, each timed by "
+                       "timing": ("fused and NCCL+cuBLAS steps alternate inside one timed loop and take turns at going first; a step is the sum of its two operations, each timed by "
                                   "its own pair of CUDA events" + (", behind an untimed device barrier over all ranks" if args.pre_barrier else ""))},
             "gemm_rs_us": round(rs_us, 2), "ag_gemm_us": round(ag_us, 2),
             "nccl_cublas_us": None if b_step_us is None else round(b_step_us, 2),

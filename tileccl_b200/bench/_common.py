@@ -61,11 +61,14 @@ def timed_series(fn, iters: int, warmup: int, before=None, flush=None) -> list[f
     return [a.elapsed_time(b) * 1e3 for a, b in zip(s, e)]
 
 
-def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=None) -> dict:
+def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=None, rotate: bool = True) -> dict:
     """Like :func:`timed_series` for several variants at once, taking one
     iteration of each in turn, so that all of them see the same clocks and
     temperature (the paired-baseline discipline of the reference,
-    comm_comp/exp1_ce_interference.cu:545-548)."""
+    comm_comp/exp1_ce_interference.cu:545-548).  With ``rotate`` the turn starts
+    one variant later every iteration, so that no variant always runs right
+    after the same neighbour (a kernel that follows a power-hungry one starts at
+    a lower clock); every rank rotates alike."""
     names = list(fns)
     for _ in range(warmup):
         for n in names:
@@ -77,7 +80,8 @@ def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=Non
     ev = {n: ([torch.cuda.Event(enable_timing=True) for _ in range(iters)],
               [torch.cuda.Event(enable_timing=True) for _ in range(iters)]) for n in names}
     for i in range(iters):
-        for n in names:
+        k = i % len(names) if rotate else 0
+        for n in names[k:] + names[:k]:
             if flush:
                 flush()
             if before:

@@ -101,7 +101,7 @@ def main(argv=None) -> int:
             runners["ctrl"] = lambda: ctrl()
         order = [o for o in C.split_csv(args.order) if o in runners]
         # One iteration of every variant in turn, so that all see the same clocks.
-        series = C.timed_interleaved({n: runners[n] for n in order}, args.iters, args.warmup, before=bar, flush=flush)
+        series = C.timed_interleaved({n: runners[n] for n in order}, args.iters, args.warmup, before=bar, flush=flush, rotate=False)   # --order is the experiment
         torch.cuda.synchronize()
         bar.check()
         fused.check()

@@ -101,8 +101,9 @@ class Sampler:
                 self.proc.kill()
 
 
-def run_step(name: str, cmd: list[str], timeout: float, out: Path, log) -> int:
-    """Runs one experiment in its own process group; on time-out the group (and only it) is killed."""
+def run_step(name: str, cmd: list[str], timeout: float, out: Path, log, manifest: bool = True) -> int:
+    """Runs one experiment in its own process group; on time-out the group (and only it) is killed.
+    ``manifest=False``: the command writes the manifest lines of its parts itself (a batched launch)."""
     t0 = time.time()
     with open(out / f"{name}.log", "w") as lf:
         lf.write("$ " + " ".join(cmd) + "\n")
@@ -119,8 +120,9 @@ def run_step(name: str, cmd: list[str], timeout: float, out: Path, log) -> int:
                 p.wait()
             rc = 124
     dur = time.time() - t0
-    with open(out / "manifest.txt", "a") as mf:
-        mf.write(f"{name} rc={rc} seconds={dur:.1f}\n")
+    if manifest or rc != 0:
+        with open(out / "manifest.txt", "a") as mf:
+            mf.write(f"{name} rc={rc} seconds={dur:.1f}\n")
     log(f"  {name}: rc={rc} in {dur:.1f} s")
     return rc
 
@@ -138,12 +140,26 @@ def done_steps(out: Path) -> set[str]:
     return ok
 
 
-def plan(n_gpus: int, quick: bool, out: Path, tuning: bool = False) -> list[tuple[str, list[str], float, int]]:
-    """(step name, command, time-out seconds, GPUs needed)."""
+class RankCmd(list):
+    """Command line of a step that runs one process per GPU through ``tileccl_b200.launch``; ``tail`` is the
+    experiment module and its flags, which is what a batched run strings together with ``--then``."""
+
+    def __init__(self, prefix: list[str], tail: list[str]):
+        super().__init__(prefix + tail)
+        self.tail = list(tail)
+
+    def __add__(self, other):
+        return RankCmd(list(self)[: len(self) - len(self.tail)], self.tail + list(other))
+
+
+def plan(n_gpus: int, quick: bool, out: Path, tuning: bool = False, iters: int = 0) -> list[tuple[str, list[str], float, int]]:
+    """(step name, command, time-out seconds, GPUs needed).  ``iters`` > 0 overrides the iteration count of
+    the fused experiments (100 in a full run, 10 in a quick one)."""
     py = sys.executable
-    launch = [py, "-m", "tileccl_b200.launch", "-n", str(max(1, n_gpus))]
+    launch = RankCmd([py, "-m", "tileccl_b200.launch", "-n", str(max(1, n_gpus))], [])
     o = str(out)
-    it = "10" if quick else "100"
+    it = str(iters) if iters > 0 else ("10" if quick else "100")
+    it2 = str(iters) if iters > 0 else ("10" if quick else "30")      # the longer-running experiments take fewer iterations
     steps = []
     # ---- fused ops (Python drivers, one process per GPU) ----
     m_sweep = ["8192", "32768"] if quick else ["512", "1024", "2048", "4096", "8192", "16384", "32768"]
@@ -159,17 +175,17 @@ def plan(n_gpus: int, quick: bool, out: Path, tuning: bool = False) -> list[tupl
     steps.append(("exp3_epilogue", launch + ["exp3_epilogue_remote", "--sizes", "8192,32768x8192x1024" if quick else "8192,8192x8192x512,512x8192x8192,32768x8192x8192,32768x8192x1024",
                                              "--iters", it, "--verify", "--csv", f"{o}/exp3_epilogue.csv"], 900, 2))
     steps.append(("exp2_ag_gemm", launch + ["exp2_ag_gemm_granularity", "--m", "32768", "--k", "8192", "--n-global", "28672", "--gather-rows", "512,4096" if quick else "128,512,2048,4096",
-                                            "--iters", "10" if quick else "30", "--verify", "--csv", f"{o}/exp2.csv"], 1200, 2))
+                                            "--iters", it2, "--verify", "--csv", f"{o}/exp2.csv"], 1200, 2))
     steps.append(("nvls_bw", launch + ["nvls_bw", "--csv", f"{o}/nvls_bw.csv"] + (["--sizes", "64K,16M,256M", "--iters", "10"] if quick else []), 600, 2))
     steps.append(("exp3_fused_nvls", launch + ["exp3_gemm_rs_fused", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it, "--transport", "nvls", "--verify",
                                                 "--csv", f"{o}/exp3_fused_nvls.csv"], 600, 2))
     if tuning:
         # knob sweeps of both fused ops at the headline shapes: all settings in one process per rank, timed in turn
-        steps.append(("tune_fused", launch + ["tune_fused", "--ops", "rs,ag", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", "10" if quick else "30",
+        steps.append(("tune_fused", launch + ["tune_fused", "--ops", "rs,ag", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it2,
                                               "--csv", f"{o}/exp3_tuning.csv"], 900, 2))
-    steps.append(("mlp_e2e", launch + ["mlp_e2e", "--iters", "10" if quick else "50", "--verify", "--csv", f"{o}/mlp_e2e.csv"], 900, 1))
+    steps.append(("mlp_e2e", launch + ["mlp_e2e", "--iters", it2 if iters > 0 or quick else "50", "--verify", "--csv", f"{o}/mlp_e2e.csv"], 900, 1))
     steps.append(("bench", [py, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={max(1, n_gpus)}", "--master-addr", "127.0.0.1", "--master-port", "29571",
-                            "bench.py", "--gpus", str(max(1, n_gpus)), "--steps", "10" if quick else "30", "--warmup", "5"], 900, 1))
+                            "bench.py", "--gpus", str(max(1, n_gpus)), "--steps", it2, "--warmup", "5"], 900, 1))
     # ---- C++ programs (single process, several GPUs) ----
     b = lambda n: str(BIN / n)  # noqa: E731
     steps.append(("exp3_fused_native", [b("exp3_gemm_rs_fused"), "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it, "--verify", "--csv", f"{o}/exp3_fused_native.csv"], 600, 2))
@@ -199,6 +215,56 @@ def plan(n_gpus: int, quick: bool, out: Path, tuning: bool = False) -> list[tupl
     return steps
 
 
+def batch_rank_steps(steps, out: Path):
+    """Merges runs of consecutive one-process-per-GPU steps into one launch each: the experiments then share one
+    set of rank processes (one interpreter start and one rendezvous instead of one per step).  ``bench/run.py``
+    writes each experiment's own manifest line and log, so the bundle looks the same as an unbatched one."""
+    merged, run = [], []
+
+    def flush():
+        if not run:
+            return
+        if len(run) == 1:
+            merged.append(run[0])
+        else:
+            head = run[0][1]
+            prefix = list(head)[: len(head) - len(head.tail)]
+            tail = ["--manifest", str(out / "manifest.txt"), "--logs", str(out)]
+            for i, (name, cmd, _to, _need) in enumerate(run):
+                tail += (["--then"] if i else []) + cmd.tail + ["--as", name]
+            merged.append((f"batch_{run[0][0]}..{run[-1][0]}", prefix + tail, sum(t for _, _, t, _ in run), max(n for _, _, _, n in run)))
+        run.clear()
+
+    for st in steps:
+        if isinstance(st[1], RankCmd):
+            run.append(st)
+        else:
+            flush()
+            merged.append(st)
+    flush()
+    return merged
+
+
+def scrub_paths(out: Path) -> None:
+    """Rewrites the text files of a bundle so that they name no directory of the machine that made them: the
+    bundle's own path becomes ``<bundle>``, the source tree ``<repo>`` and the interpreter ``python``."""
+    subs = [(str(out), "<bundle>"), (str(PKG.parent.resolve()), "<repo>"), (str(PKG.parent), "<repo>"), (sys.executable, "python"),
+            (os.path.realpath(sys.executable), "python")]
+    subs = sorted(set(s for s in subs if s[0]), key=lambda kv: -len(kv[0]))
+    for p in out.rglob("*"):
+        if not p.is_file() or p.suffix not in (".log", ".txt", ".csv", ".md"):
+            continue
+        try:
+            text = p.read_text()
+        except (UnicodeDecodeError, OSError):
+            continue
+        new = text
+        for a, b in subs:
+            new = new.replace(a, b)
+        if new != text:
+            p.write_text(new)
+
+
 def load_clock_check(out: Path, log) -> None:
     """Records what the SM clock does under a sustained GEMM (read-only: nothing is locked)."""
     code = ("import torch,time;a=torch.randn(8192,8192,device='cuda',dtype=torch.bfloat16);b=a.clone();"
@@ -220,12 +286,14 @@ def main(argv=None) -> int:
     ap.add_argument("--only", default=None, help="comma list of step-name prefixes")
     ap.add_argument("--list", action="store_true")
     ap.add_argument("--tuning", action="store_true", help="add the knob sweeps of the two fused ops (step tune_fused, CSV exp3_tuning.csv)")
+    ap.add_argument("--iters", type=int, default=0, help="iteration count of the fused experiments (default: 100, or 10 with --quick)")
+    ap.add_argument("--batch", action="store_true", help="run consecutive one-process-per-GPU experiments in one set of rank processes")
     ap.add_argument("--keep", action="store_true", help="do not zip the bundle")
     ap.add_argument("--ncu", action="store_true", help="also capture the NVLink section of one peer_l2_probe launch with ncu (off by default; needs profiling permission)")
     args = ap.parse_args(argv)
     out = Path(args.resume or args.out or f"reports/results_{time.strftime('%Y%m%d_%H%M%S')}").resolve()
     n = gpu_count()
-    steps = plan(n, args.quick, out, tuning=args.tuning)
+    steps = plan(n, args.quick, out, tuning=args.tuning, iters=args.iters)
     if args.ncu and shutil.which("ncu"):
         # One small single-launch capture, one GPU's kernel, clocks left alone.  The plain command runs first.
         once = [str(BIN / "peer_l2_probe"), "--modes", "once", "--targets", "peer", "--sizes", "256M", "--total", "1G", "--no-verify"]
@@ -265,6 +333,7 @@ def main(argv=None) -> int:
             load_clock_check(out, log)
         skip = done_steps(out) if args.resume else set()
         worst = 0
+        todo = []
         for name, cmd, to, need in steps:
             if name in skip:
                 log(f"  {name}: already done, skipped")
@@ -274,7 +343,11 @@ def main(argv=None) -> int:
                     mf.write(f"{name} rc=skipped needs={need}gpus\n")
                 log(f"  {name}: skipped (needs {need} GPUs, have {n})")
                 continue
-            worst = max(worst, run_step(name, cmd, to, out, log))
+            todo.append((name, cmd, to, need))
+        if args.batch:
+            todo = batch_rank_steps(todo, out)
+        for name, cmd, to, need in todo:
+            worst = max(worst, run_step(name, cmd, to, out, log, manifest=not name.startswith("batch_")))
     finally:
         if sampler:
             sampler.stop()
@@ -284,12 +357,13 @@ def main(argv=None) -> int:
         (out / "verdict.txt").write_text(analyze.report(str(out)))
     except Exception as e:  # noqa: BLE001
         (out / "verdict.txt").write_text(f"analysis failed: {e}\n")
+    log(f"done, worst rc {worst}")
+    scrub_paths(out)
     if not args.keep:
         with zipfile.ZipFile(str(out) + ".zip", "w", zipfile.ZIP_DEFLATED) as z:
             for p in sorted(out.rglob("*")):
                 if p.is_file():
                     z.write(p, p.relative_to(out.parent))
-    log(f"done, worst rc {worst}")
     return 0 if worst == 0 else 1
 
 
