@@ -80,10 +80,10 @@ def check_gemm_rs(heap, fails, tag, M, N, K, cta_group, iters=3, poison=True, fi
     return True
 
 
-def check_ag_gemm(heap, fails, tag, M, N, K, cta_group, gather_rows, transport, iters=3):
+def check_ag_gemm(heap, fails, tag, M, N, K, cta_group, gather_rows, transport, iters=3, **kw):
     world = heap.world
     Bt = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
-    op = AgGemm(heap, M, K, Bt, cta_group=cta_group, gather_rows=gather_rows, timeout_ms=2000, transport=transport)
+    op = AgGemm(heap, M, K, Bt, cta_group=cta_group, gather_rows=gather_rows, timeout_ms=2000, transport=transport, **kw)
     for it in range(iters):
         shard = torch.randn(M // world, K, device="cuda", dtype=torch.bfloat16)
         # poison the peers' part of the gathered buffer: stale rows must not be used
@@ -209,6 +209,15 @@ def main():
             torch.cuda.synchronize()
             dist.barrier()
             heap._cursor = mark
+        # knobs: one fence per tile / per 16 tiles in the signalling warp; two gather warps moving 32 bytes per instruction
+        for sb in (1, 16):
+            ok = ok and check_gemm_rs(heap, fails, f"g{cta_group} large, signal batch {sb}", Ml, 4096, 512, cta_group, iters=2, signal_batch=sb)
+            heap._cursor = mark
+        ok = ok and check_ag_gemm(heap, fails, f"g{cta_group} large, 2 gather warps, 32-byte moves", Ml, 4096, 1024, cta_group, 1024, "pull", iters=2,
+                                  gather_warps=2, vec32=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        heap._cursor = mark
 
     # ---- through the NVSwitch, when multicast is available ----
     from tileccl_b200 import _native

@@ -66,3 +66,31 @@ def test_static_entry_point_matches_the_allocating_one_twice():
     assert L.tcl_max_rel_err_static(got.data_ptr(), ref.data_ptr(), 5000, res.data_ptr(), stream) == 0
     torch.cuda.synchronize()
     assert float(res) > 1e38 and ew.max_rel_err(got, ref) > 1e38
+
+
+@pytest.mark.gpu
+def test_static_entry_point_at_its_size_limit_on_a_side_stream():
+    """The largest problem the array serves (all 16384 slots in use), issued on a stream other than the
+    default one; then a small problem on the same stream, which must not see the large one's slots."""
+    import torch
+    from tileccl_b200.ops import elementwise as ew
+    L = _lib()
+    torch.manual_seed(12)
+    side = torch.cuda.Stream()
+    n = MAX_ELEMS - 7
+    ref = torch.randn(n, device="cuda")
+    got = ref.bfloat16()
+    got[n - 3] = 400.0                                   # the worst element sits in the last block
+    want = ew.max_rel_err(got, ref)
+    res = torch.zeros(2, device="cuda")
+    small_ref = torch.randn(4097, device="cuda")
+    small_got = (small_ref + 0.01).bfloat16()
+    small_want = ew.max_rel_err(small_got, small_ref)
+    torch.cuda.synchronize()
+    sp = C.c_void_p(side.cuda_stream)
+    with torch.cuda.stream(side):
+        assert L.tcl_max_rel_err_static(got.data_ptr(), ref.data_ptr(), n, res.data_ptr(), sp) == 0
+        assert L.tcl_max_rel_err_static(small_got.data_ptr(), small_ref.data_ptr(), 4097, res.data_ptr() + 4, sp) == 0
+    side.synchronize()
+    assert abs(float(res[0]) - want) <= 1e-6 * max(1.0, abs(want)) and float(res[0]) > 10.0
+    assert abs(float(res[1]) - small_want) <= 1e-6

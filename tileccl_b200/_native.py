@@ -65,6 +65,8 @@ class GemmDesc(C.Structure):
         ("ablate", C.c_int32),
         ("epi_st256", C.c_int32),
         ("epi_tma_store", C.c_int32),
+        ("rs_signal_batch", C.c_int32),
+        ("ag_vec32", C.c_int32),
         ("ag_warps", C.c_int32),
         ("epoch_dev", C.c_void_p),
     ]

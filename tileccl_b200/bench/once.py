@@ -6,6 +6,8 @@ profiling with ncu (small case, few launches).
     python -m tileccl_b200.bench.once silu_mul --m 16384 --n 3584
     python -m tileccl_b200.bench.once ag_gemm --m 8192 --n 7168 --k 8192 --epi silu_mul   (world of one: flag-gated
                                                     producer, gather warps idle, fused SiLU(gate)*up epilogue)
+    python -m tileccl_b200.bench.once barrier                      (the device barrier kernel, world of one)
+    python -m tileccl_b200.bench.once p2p_copy --m 16384 --n 8192  (the flat 16-byte mover of nvls_bw, local to local)
 
 The reference's counterpart is ``peer_l2_probe --modes once`` (l2_peer_cache/peer_l2_probe.cu:53-58).
 """
@@ -26,7 +28,7 @@ from . import _common as C
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "gemm_rs", "silu_mul", "ag_gemm"])
+    ap.add_argument("what", choices=["gemm", "gemm_rs", "silu_mul", "ag_gemm", "barrier", "p2p_copy"])
     ap.add_argument("--m", type=C.parse_size, default=8192)
     ap.add_argument("--n", type=C.parse_size, default=8192)
     ap.add_argument("--k", type=C.parse_size, default=8192)
@@ -36,7 +38,22 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     dev = torch.device("cuda", torch.cuda.current_device())
     M, N, K = args.m, args.n, args.k
-    if args.what == "silu_mul":
+    if args.what == "barrier":
+        heap = SymmetricHeap(8 << 20)
+        bar = ew.DeviceBarrier(heap)
+        run, check = bar, bar.check
+    elif args.what == "p2p_copy":
+        import ctypes as C_
+
+        from .. import _native
+        src = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        dst = torch.empty_like(src)
+        ew.fill_normal_(src, seed=3)
+        lib = _native.lib()
+        run = lambda: _native.check(lib.tcl_p2p_copy(C_.c_void_p(dst.data_ptr()), C_.c_void_p(src.data_ptr()), src.numel() * 2, 0,
+                                                     C_.c_void_p(torch.cuda.current_stream().cuda_stream)), "p2p_copy")
+        check = lambda: None
+    elif args.what == "silu_mul":
         gu = torch.empty(M, 2 * N, dtype=torch.bfloat16, device=dev)
         ew.fill_normal_(gu, seed=1)
         out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)

@@ -41,15 +41,19 @@ RS_SETTINGS: dict[str, dict] = {
     "gm4": {"group_m": 4}, "gm16": {"group_m": 16}, "gm32": {"group_m": 32},
     "chunks1": {"rs_chunks": 1}, "chunks4": {"rs_chunks": 4}, "chunks8": {"rs_chunks": 8},
     "ctas128": {"num_ctas": 128}, "ctas96": {"num_ctas": 96}, "ctas64": {"num_ctas": 64},
-    "cg1": {"cta_group": 1},
-    "nvls": {"transport": "nvls"},
+    "sb1": {"signal_batch": 1}, "sb2": {"signal_batch": 2}, "sb8": {"signal_batch": 8}, "sb16": {"signal_batch": 16},
+    "cg1": {"cta_group": 1}, "cg1_sb1": {"cta_group": 1, "signal_batch": 1}, "cg1_sb8": {"cta_group": 1, "signal_batch": 8},
+    "nvls": {"transport": "nvls"}, "nvls_sb1": {"transport": "nvls", "signal_batch": 1},
     "noreduce": {"ablate": 1}, "nosignal": {"ablate": 3},
 }
 AG_SETTINGS: dict[str, dict] = {
     "default": {},
     "gr128": {"gather_rows": 128}, "gr2048": {"gather_rows": 2048}, "gr4096": {"gather_rows": 4096},
     "item8": {"item_rows": 8},
-    "gw2": {"gather_warps": 2}, "gw1": {"gather_warps": 1},
+    "gw2": {"gather_warps": 2}, "gw3": {"gather_warps": 3}, "v32": {"vec32": True}, "gw2_v32": {"gather_warps": 2, "vec32": True},
+    "gw2_v32_gm16": {"gather_warps": 2, "vec32": True, "group_m": 16},
+    "gw2_gm16": {"gather_warps": 2, "group_m": 16}, "gw2_gm16_gr2048": {"gather_warps": 2, "group_m": 16, "gather_rows": 2048},
+    "gw2_gr4096": {"gather_warps": 2, "gather_rows": 4096}, "gm16_gr2048": {"group_m": 16, "gather_rows": 2048},
     "gm4": {"group_m": 4}, "gm16": {"group_m": 16},
     "cg1": {"cta_group": 1},
     "push": {"transport": "push"},
@@ -146,7 +150,7 @@ def main(argv=None) -> int:
             _sweep("gemm_rs", names, RS_SETTINGS, lambda kw: GemmRs(mc_heap if kw.get("transport") == "nvls" else heap, A, Bt, **kw),
                    lambda: base_ops.gemm_rs_baseline(A, Bt, out=out_nccl, full=D), heap, args,
                    roofline.gemm_rs_roofline_us(M, N, K, world), (M, N, K),
-                   {"cta_group": 2, "transport": "p2p", "rs_chunks": 0, "group_m": 0, "num_ctas": 0, "st256": 0, "ablate": 0}, rank, world)
+                   {"cta_group": 2, "transport": "p2p", "rs_chunks": 0, "group_m": 0, "num_ctas": 0, "st256": 0, "signal_batch": 0, "ablate": 0}, rank, world)
             torch.cuda.synchronize()
             G.host_barrier()
         except BaseException:
@@ -178,7 +182,7 @@ def main(argv=None) -> int:
 
         _sweep("ag_gemm", names, AG_SETTINGS, build, lambda: base_ops.ag_gemm_baseline(shard, Bt, gathered=gathered, out=out_b), heap, args,
                roofline.ag_gemm_roofline_us(M, N, K, world), (M, N, K),
-               {"cta_group": 2, "transport": "pull", "gather_rows": 512, "item_rows": 1, "group_m": 0, "ablate": 0, "comm_enabled": 1}, rank, world)
+               {"cta_group": 2, "transport": "pull", "gather_rows": 512, "item_rows": 1, "gather_warps": 0, "group_m": 0, "ablate": 0, "comm_enabled": 1}, rank, world)
         torch.cuda.synchronize()
         G.host_barrier()
         heap.close()

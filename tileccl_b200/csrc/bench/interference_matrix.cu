@@ -8,7 +8,8 @@
 // the hbm probe's buffer.  The mover's bandwidth alone is measured once per mover and reused for every probe
 // unless --no-alone-cache asks for a fresh figure beside each pair.  --mode starve fills every SM with a
 // squatter kernel and shows what each mover does when it gets no SM (the squatter leaves after --starve-ms,
-// one second by default, at the latest).
+// one second by default, at the latest).  --mode once launches every probe once, alone, for --window-ms: the
+// form a profiler can capture.
 //
 // Reference parity: tests/interference_matrix.cu (movers :174-254, probes :282-377, probe context
 // :558-670, matrix :846-946, starve :950-1029, CSV header :839-841).
@@ -204,7 +205,7 @@ int main(int argc, char** argv) {
     else if (f == "--dst") dst = std::atoi(need().c_str());
     else if (f == "--csv") csv_path = need();
     else {
-      std::printf("usage: %s [--mode matrix|starve] [--probes LIST] [--comms ce,tma,reg] [--probe-dev src|dst] [--comm-sms N] [--probe-sms N]\n"
+      std::printf("usage: %s [--mode matrix|starve|once] [--probes LIST] [--comms ce,tma,reg] [--probe-dev src|dst] [--comm-sms N] [--probe-sms N]\n"
                   "          [--msg B] [--total B] [--hbm-buf B] [--iters N] [--window-ms N] [--starve-ms MS] [--no-alone-cache] [--reg-threads N]\n"
                   "          [--stages 3|4|6|8] [--src N] [--dst N] [--csv FILE]\n", argv[0]);
       return f == "-h" || f == "--help" ? 0 : 1;
@@ -241,6 +242,19 @@ int main(int argc, char** argv) {
   if (!csv.open(csv_path, "mode,probe,comm,probe_dev,probe_sms,comm_sms,msg_bytes,comm_alone_gbps,comm_ovl_gbps,S_m,probe_alone,probe_ovl,unit,S_c")) return 1;
   auto kind_of = [&](const std::string& p) { for (int k = 0; k < kProbeCount; ++k) if (p == probe_name(k)) return k; return -1; };
 
+  if (mode == "once") {
+    // For a profiler: every probe is launched once, alone, for --window-ms, and ends on its own deadline; nothing is
+    // measured and the host does not touch the kernel while it runs.
+    const int nb = probe_sms > 0 ? std::min(probe_sms, pc.sms) : pc.sms;
+    for (auto& p : probes) {
+      const int k = kind_of(p);
+      if (k < 0) { std::fprintf(stderr, "unknown probe %s\n", p.c_str()); return 1; }
+      pc.launch(k, nb, static_cast<double>(window_ms), l2);
+      TCL_CUDA_CHECK(cudaStreamSynchronize(pc.st));
+      std::printf("once: %s probe, %d CTAs, %d ms\n", p.c_str(), nb, window_ms);
+    }
+    return 0;
+  }
   if (mode == "starve") {
     // Squatter: as many FFMA CTAs as the GPU can hold, for at most one second.
     int per_sm = 0;

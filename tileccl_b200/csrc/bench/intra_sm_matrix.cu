@@ -175,11 +175,13 @@ int main(int argc, char** argv) {
   int warps = 16, blocks = 0, comm_ctas = 0, window_ms = 300, src = 0, dst = 1;
   size_t msg = 16384, cbuf = size_t(64) << 20, pbuf = size_t(256) << 20;
   std::string csv_path;
+  bool once = false;
   Args a(argc, argv);
   while (a.more()) {
     std::string f = a.flag(), v;
     auto need = [&]() { if (!a.value(&v)) std::exit(1); return v; };
     if (f == "--probes") probes = split_csv(need());
+    else if (f == "--once") once = true;
     else if (f == "--comms") comms = split_csv(need());
     else if (f == "--comm-warps") parse_int_list(need(), &comm_warps);
     else if (f == "--warps") warps = std::atoi(need().c_str());
@@ -194,7 +196,9 @@ int main(int argc, char** argv) {
     else if (f == "--csv") csv_path = need();
     else {
       std::printf("usage: %s [--probes mma,ffma,smem,hbm] [--comms ldst,tma] [--comm-warps LIST] [--warps N] [--blocks N] [--comm-ctas N]\n"
-                  "          [--msg B] [--cbuf B] [--pbuf B] [--window-ms MS] [--src N] [--dst N] [--csv FILE]\n", argv[0]);
+                  "          [--msg B] [--cbuf B] [--pbuf B] [--window-ms MS] [--src N] [--dst N] [--csv FILE] [--once]\n"
+                  "--once: for a profiler: every (probe, comm, comm-warps) combination is launched once for --window-ms and left to end on\n"
+                  "        its own time budget; nothing is measured and the host does not touch the kernel while it runs\n", argv[0]);
       return f == "-h" || f == "--help" ? 0 : 1;
     }
   }
@@ -274,6 +278,29 @@ int main(int argc, char** argv) {
     return o;
   };
 
+  if (once) {
+    for (auto& pn : probes) {
+      int pid = -1;
+      for (int k = 0; k < 4; ++k) if (pn == kProbeNames[k]) pid = k;
+      if (pid < 0) { std::fprintf(stderr, "unknown probe %s\n", pn.c_str()); return 1; }
+      for (auto& cn : comms) {
+        const int cid = cn == "tma" ? kCommTma : kCommLdst;
+        if (cid == kCommTma && !tma_ok) continue;
+        for (int cw : comm_warps) {
+          if (cw < 1 || cw >= warps) continue;
+          fa.probe = pid; fa.comm = cid; fa.comm_warps = cw;
+          fa.budget_ns = static_cast<unsigned long long>(window_ms) * 1000000ull;
+          TCL_CUDA_CHECK(cudaMemsetAsync(stop_d, 0, 4, st));
+          TCL_CUDA_CHECK(cudaMemsetAsync(cnt_d, 0, 64, st));
+          fused_kernel<<<blocks, warps * 32, cid == kCommTma ? dyn_smem : 0, st>>>(fa);
+          TCL_CUDA_CHECK(cudaGetLastError());
+          TCL_CUDA_CHECK(cudaStreamSynchronize(st));
+          std::printf("once: %s x %s, %d comm warps, %d ms\n", pn.c_str(), cn.c_str(), cw, window_ms);
+        }
+      }
+    }
+    return 0;
+  }
   Csv csv;
   if (!csv.open(csv_path, "probe,comm,warps,comm_warps,comm_ctas,msg_bytes,comm_gbps,full,base,ovl,unit,S_warp,S_intra,S_pure")) return 1;
   std::printf("# intra_sm_matrix: %d CTAs x %d warps, msg %zu B, window %d ms, comm-ctas %d\n", blocks, warps, msg, window_ms, comm_ctas);

@@ -115,6 +115,8 @@ struct GemmParams {
   const __nv_bfloat16* rs_stage;      // this rank's staging [world][seg_rows][N]
   __nv_bfloat16* rs_out;              // this rank's reduced shard [seg_rows][ld_out]
   int ld_out;
+  int rs_signal_batch;                // finished tiles the signalling warp lets accumulate before it fences and signals
+                                      // (the last tiles of the CTA are always signalled at once)
   // NVLS variant: partial tiles stay in the producer's own full-size staging [M][N]; the owner's reduce
   // warps read this multicast address of it, and the NVSwitch returns the sum over all ranks.
   const __nv_bfloat16* rs_mc_stage;   // multicast mapping of the staging buffer, or nullptr (P2P push)
@@ -127,6 +129,7 @@ struct GemmParams {
   int ag_item_rows;                        // rows one gather warp moves per work item (and per counter arrival);
                                            // small items make rows land progressively, in schedule order
   int ag_warps;                            // gather warps per CTA that take part (1..4); the others idle
+  int ag_vec32;                            // pull form: 32-byte loads and stores (needs K % 16 == 0) instead of 16-byte ones
   int* ag_done;                            // local: gather warps that finished (monotonic)
   int* ag_read_done[kMaxWorld];            // rank s's "peers done reading me" counter
   // Push form of the all-gather: every rank stores its own shard into every peer's gathered buffer.
@@ -266,6 +269,57 @@ __device__ __forceinline__ void reduce_tile_nvls(const __nv_bfloat16* mc_tile, i
     for (int j = 0; j < 8; ++j) w[j] = ptx::multimem_ld_reduce_bf16x8(mc_tile + static_cast<size_t>((pass + j) * 4 + r_base) * ldn);
 #pragma unroll
     for (int j = 0; j < 8; ++j) ptx::st_v4(out + out_off + static_cast<size_t>((pass + j) * 4 + r_base) * ld_out, w[j]);
+  }
+}
+
+// One warp copies `item_bytes` (a multiple of sizeof(V)) from a peer's memory to local memory with loads that do not
+// allocate in L1.  Two register banks of kUnroll vectors per lane: the loads of one step (kUnroll * 32 lanes *
+// sizeof(V) = 4 KiB) are issued before the previous step is stored, so 4 to 8 KiB of peer loads per warp are
+// always in flight.  V = uint4 moves 16 bytes per instruction, V = Vec8 32 bytes (half the instructions; the
+// addresses must then be 32-byte aligned).
+__device__ __forceinline__ void ld_item(uint4& v, const char* p) { v = ptx::ld_v4_stream(p); }
+__device__ __forceinline__ void ld_item(ptx::Vec8& v, const char* p) { v = ptx::ld_v8_stream(p); }
+__device__ __forceinline__ void st_item(char* p, const uint4& v) { ptx::st_v4(p, v); }
+__device__ __forceinline__ void st_item(char* p, const ptx::Vec8& v) { ptx::st_v8(p, v); }
+
+template <typename V, int kUnroll>
+__device__ __forceinline__ void copy_item(const char* __restrict__ src, char* __restrict__ dst, size_t item_bytes, int lane) {
+  constexpr size_t kRow = 32 * sizeof(V);          // bytes one warp-wide instruction moves
+  constexpr size_t kStep = kUnroll * kRow;
+  size_t off = static_cast<size_t>(lane) * sizeof(V);
+  auto fits = [&](size_t o) { return o + (kUnroll - 1) * kRow < item_bytes; };
+  if (fits(off)) {
+    V wa[kUnroll], wb[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) ld_item(wa[u], src + off + u * kRow);
+    size_t nxt = off + kStep;
+    for (;;) {
+      bool more = fits(nxt);
+      if (more) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) ld_item(wb[u], src + nxt + u * kRow);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) st_item(dst + off + u * kRow, wa[u]);
+      off = nxt;
+      nxt += kStep;
+      if (!more) break;
+      more = fits(nxt);
+      if (more) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) ld_item(wa[u], src + nxt + u * kRow);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) st_item(dst + off + u * kRow, wb[u]);
+      off = nxt;
+      nxt += kStep;
+      if (!more) break;
+    }
+  }
+  for (; off < item_bytes; off += kRow) {
+    V v;
+    ld_item(v, src + off);
+    st_item(dst + off, v);
   }
 }
 
@@ -789,41 +843,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!detail::in_range(p, s_abort, seg, src, static_cast<unsigned>(item_bytes))) continue;
           const size_t grow = static_cast<size_t>(seg) * p.seg_rows + row_in_seg;
           char* dst = reinterpret_cast<char*>(p.ag_full + grow * p.K);
-          // Two register banks of 8 x 16 bytes per lane: the loads of one 4 KiB step are issued
-          // before the previous step is stored, so 8 to 16 peer loads per lane are always in flight.
-          constexpr int kUnroll = 8;
-          constexpr size_t kStep = kUnroll * 512;
-          size_t off = static_cast<size_t>(lane) * 16;
-          auto fits = [&](size_t o) { return o + (kUnroll - 1) * 512 < item_bytes; };
-          if (fits(off)) {
-            uint4 wa[kUnroll], wb[kUnroll];
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) wa[u] = ld_v4_stream(src + off + u * 512);
-            size_t nxt = off + kStep;
-            for (;;) {
-              bool more = fits(nxt);
-              if (more) {
-#pragma unroll
-                for (int u = 0; u < kUnroll; ++u) wb[u] = ld_v4_stream(src + nxt + u * 512);
-              }
-#pragma unroll
-              for (int u = 0; u < kUnroll; ++u) st_v4(dst + off + u * 512, wa[u]);
-              off = nxt;
-              nxt += kStep;
-              if (!more) break;
-              more = fits(nxt);
-              if (more) {
-#pragma unroll
-                for (int u = 0; u < kUnroll; ++u) wa[u] = ld_v4_stream(src + nxt + u * 512);
-              }
-#pragma unroll
-              for (int u = 0; u < kUnroll; ++u) st_v4(dst + off + u * 512, wb[u]);
-              off = nxt;
-              nxt += kStep;
-              if (!more) break;
-            }
-          }
-          for (; off < item_bytes; off += 512) st_v4(dst + off, ld_v4_stream(src + off));
+          if (p.ag_vec32) detail::copy_item<Vec8, 4>(src, dst, item_bytes, lane);
+          else detail::copy_item<uint4, 8>(src, dst, item_bytes, lane);
           // The consumer of these rows is TMA (async proxy) on another SM.
           fence_proxy_async();
           __syncwarp();
@@ -860,6 +881,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int signalled = 0;
       int t = group_id;
       unsigned spins = 0;
+      // A fence at system scope holds this SM's stores back until the peers have acknowledged everything in
+      // flight (a link round trip), so it is not taken per tile: finished tiles accumulate up to a batch, and the
+      // tail of this CTA's tile list goes out as soon as it is stored.
+      const int my_tiles = group_id < num_tiles ? (num_tiles - group_id + num_groups - 1) / num_groups : 0;
+      const int batch = p.rs_signal_batch > 0 ? p.rs_signal_batch : 1;
       while (t < num_tiles) {
         // A tile is finished when every epilogue warp has stored its 32 rows of it.  The warps are not in
         // lock step (a warp may be a tile or two ahead of the slowest one), so the count is the minimum of
@@ -867,7 +893,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int done = s_warp_tiles[0];
 #pragma unroll
         for (int w = 1; w < Cfg::EPI_WARPS; ++w) done = min(done, s_warp_tiles[w]);
-        if (done > signalled) {
+        if (done - signalled >= batch || (done > signalled && done == my_tiles)) {
           fence_sys();
           for (; signalled < done && t < num_tiles; ++signalled, t += num_groups) {
             int m_blk, n_blk;

@@ -14,6 +14,9 @@ namespace {
 
 using namespace tcl;
 
+// Finished tiles per system-scope fence of the GEMM+RS signalling warp when the caller does not say.
+constexpr int kDefaultRsSignalBatch = 4;
+
 struct GemmPlan {
   CUtensorMap tmap_a;
   CUtensorMap tmap_b;
@@ -198,7 +201,7 @@ int tcl_gemm_desc_offset(const char* field) {
   TCL_OFF(mode) TCL_OFF(M) TCL_OFF(lda) TCL_OFF(A) TCL_OFF(world) TCL_OFF(seg_rows) TCL_OFF(dst_base) TCL_OFF(dst_row_off)
   TCL_OFF(rs_tile_cnt) TCL_OFF(rs_stage) TCL_OFF(rs_chunks) TCL_OFF(ag_src) TCL_OFF(ag_flags) TCL_OFF(gather_rows) TCL_OFF(ag_done)
   TCL_OFF(ag_push) TCL_OFF(ag_dst) TCL_OFF(barrier) TCL_OFF(status) TCL_OFF(timeout_ns) TCL_OFF(group_m) TCL_OFF(rs_mc_stage)
-  TCL_OFF(range_lo) TCL_OFF(epi_silu_mul) TCL_OFF(ablate) TCL_OFF(epi_st256) TCL_OFF(epi_tma_store) TCL_OFF(epoch_dev) TCL_OFF(ag_warps)
+  TCL_OFF(range_lo) TCL_OFF(epi_silu_mul) TCL_OFF(ablate) TCL_OFF(epi_st256) TCL_OFF(epi_tma_store) TCL_OFF(epoch_dev) TCL_OFF(ag_warps) TCL_OFF(rs_signal_batch) TCL_OFF(ag_vec32)
 #undef TCL_OFF
   return -1;
 }
@@ -332,6 +335,7 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
     p.rs_out = static_cast<__nv_bfloat16*>(d->rs_out);
     p.ld_out = d->ld_out;
     p.rs_mc_stage = static_cast<const __nv_bfloat16*>(d->rs_mc_stage);
+    p.rs_signal_batch = d->rs_signal_batch > 0 ? d->rs_signal_batch : kDefaultRsSignalBatch;
   } else if (d->mode == TCL_MODE_AG_GEMM) {
     if (nseg != d->world) return fail("AG+GEMM: M / seg_rows must equal world");
     if (d->lda != d->K) return fail("AG+GEMM: gathered A must be dense (lda == K)");
@@ -360,6 +364,11 @@ void* tcl_gemm_plan_create(const tcl_gemm_desc* d, char* err, int errlen) {
     p.gather_rows = d->gather_rows > 0 ? d->gather_rows : d->seg_rows;
     p.ag_done = d->ag_done;
     p.ag_item_rows = d->ag_item_rows > 0 ? d->ag_item_rows : 1;
+    p.ag_vec32 = d->ag_vec32 ? 1 : 0;
+    if (p.ag_vec32 && (d->K % 16 != 0 || (reinterpret_cast<uintptr_t>(d->A) & 31))) return fail("AG+GEMM: ag_vec32 needs K % 16 == 0 and a 32-byte aligned gathered buffer");
+    if (p.ag_vec32 && d->comm_enabled && d->world > 1)
+      for (int s = 0; s < d->world; ++s)
+        if (reinterpret_cast<uintptr_t>(d->ag_src[s]) & 31) return fail("AG+GEMM: ag_vec32 needs 32-byte aligned ag_src");
     p.ag_warps = d->ag_warps > 0 ? d->ag_warps : GemmCfg<1>::COMM_WARPS;
     if (p.ag_warps > GemmCfg<1>::COMM_WARPS) return fail("AG+GEMM: ag_warps must lie in 1..4");
     if (p.gather_rows % p.ag_item_rows != 0) return fail("AG+GEMM: ag_item_rows must divide gather_rows");

@@ -65,6 +65,8 @@ typedef struct tcl_gemm_desc {
                            32-byte aligned and ldc a multiple of 16 elements; not with epi_silu_mul */
   int32_t epi_tma_store; /* the epilogue leaves through TMA (cp.async.bulk.tensor stores from the staging buffer) instead of
                             st.global; plain and AG+GEMM modes and the non-communicating GEMM+RS; not with epi_silu_mul */
+  int32_t rs_signal_batch; /* GEMM+RS: finished tiles per system-scope fence of the signalling warp; 0 = default */
+  int32_t ag_vec32;      /* AG+GEMM pull: gather with 32-byte loads/stores (K % 16 == 0 and 32-byte aligned buffers) */
   int32_t ag_warps;      /* AG+GEMM: gather warps per CTA that take part, 1..4; 0 = all four */
   int32_t* epoch_dev;    /* optional: two zeroed ints in device memory.  When set, the kernel takes the call number from
                             epoch_dev[0] + 1 (and advances it when the call ends) instead of the `epoch` argument of

@@ -34,7 +34,9 @@ def heap_bytes(tokens: int, hidden: int, ffn: int, world: int) -> int:
 class TpMlp:
     def __init__(self, heap: SymmetricHeap, tokens: int, hidden: int = 8192, ffn: int = 28672,
                  cta_group: int = 2, gather_rows: int = 512, seed: int = 0, init_std: float = 0.02,
-                 fuse_silu: bool = True, graph: bool = False):
+                 fuse_silu: bool = True, graph: bool = False, num_ctas: int = 0):
+        """``num_ctas`` caps the grid of both kernels (0 = one CTA per SM): the all-gather GEMM needs all its
+        CTAs resident at once, so a caller that runs other kernels beside the block leaves them SMs this way."""
         world, rank = heap.world, heap.rank
         if ffn % world or tokens % world:
             raise ValueError("ffn and tokens must be divisible by the world size")
@@ -53,12 +55,12 @@ class TpMlp:
         if self.fuse_silu:
             self.h = None
             self.ag = AgGemm(heap, tokens, hidden, self.w_gate_up, cta_group=cta_group,
-                             gather_rows=gather_rows, out=self.act, epi="silu_mul", device_epoch=graph)
+                             gather_rows=gather_rows, out=self.act, epi="silu_mul", device_epoch=graph, num_ctas=num_ctas)
         else:
             self.h = torch.empty(tokens, 2 * f, dtype=torch.bfloat16, device=dev)
             self.ag = AgGemm(heap, tokens, hidden, self.w_gate_up, cta_group=cta_group,
-                             gather_rows=gather_rows, out=self.h, device_epoch=graph)
-        self.rs = GemmRs(heap, self.act, self.w_down, cta_group=cta_group, device_epoch=graph)
+                             gather_rows=gather_rows, out=self.h, device_epoch=graph, num_ctas=num_ctas)
+        self.rs = GemmRs(heap, self.act, self.w_down, cta_group=cta_group, device_epoch=graph, num_ctas=num_ctas)
         self._graph = None
         self._want_graph = graph
 

@@ -12,6 +12,15 @@ that rows land progressively in the order the tile schedule consumes them).
 instead; measured at 8 GPUs it is slower than pull (2.0 ms against 1.38 ms on
 the 32768 x 3584 x 8192 case) and is kept as the measured alternative.
 
+Co-residency: the gather work is dealt over the gather warps of every CTA of the grid, and every CTA's
+TMA producer waits for row blocks that other CTAs gather.  The kernel therefore needs all its CTAs resident
+at the same time: one CTA per SM, grid <= number of SMs that are free.  If another kernel holds SMs while
+this one runs (an NCCL kernel, a copy kernel on a second stream), resident CTAs wait for CTAs that cannot
+start, and the call ends with the "gathered row block never arrived" status after the time-out instead of
+hanging.  Callers that overlap other kernels pass ``num_ctas`` (a multiple of ``cta_group``) small enough to
+leave those kernels their SMs.  The fused GEMM + reduce-scatter has the same requirement across ranks only
+(its reduce warps wait for peers, not for other CTAs of the same grid).
+
 Reference parity: comm_comp/exp2_ag_gemm_granularity.cu:168-300 (the
 segmented-launch + copy-engine pipeline; its chunk count S is this op's
 ``gather_rows``), and :15-20 of that file for the in-kernel form built here.
@@ -30,7 +39,7 @@ class AgGemm:
     def __init__(self, heap: SymmetricHeap, M: int, K: int, Bt: torch.Tensor, cta_group: int = 2,
                  gather_rows: int = 512, out: torch.Tensor | None = None, group_m: int = 0,
                  num_ctas: int = 0, comm_enabled: bool = True, timeout_ms: float = 4000.0, ablate: int = 0, transport: str = "pull", item_rows: int = 1, epi: str | None = None,
-                 device_epoch: bool = False, hold_operands: bool = True, gather_warps: int = 0):
+                 device_epoch: bool = False, hold_operands: bool = True, gather_warps: int = 0, vec32: bool = False):
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
         world, rank = heap.world, heap.rank
@@ -85,6 +94,7 @@ class AgGemm:
         d.gather_rows = gather_rows
         d.ag_item_rows = item_rows
         d.ag_warps = gather_warps          # gather warps per CTA that take part (0 = all four)
+        d.ag_vec32 = 1 if vec32 else 0     # 32-byte gather loads and stores instead of 16-byte ones
         self.item_rows = item_rows
         d.ag_done = self.done.data_ptr()
         d.timeout_ns = int(timeout_ms * 1e6)

@@ -29,7 +29,7 @@ class GemmRs:
     def __init__(self, heap: SymmetricHeap, A: torch.Tensor, Bt: torch.Tensor, cta_group: int = 2,
                  rs_chunks: int = 0, comm_enabled: bool = True, group_m: int = 0, num_ctas: int = 0,
                  timeout_ms: float = 4000.0, ablate: int = 0, force_staged: bool = False, transport: str = "p2p",
-                 st256: bool = False, device_epoch: bool = False, hold_operands: bool = True):
+                 st256: bool = False, device_epoch: bool = False, hold_operands: bool = True, signal_batch: int = 0):
         require_bf16_rowmajor(A, "A")
         require_bf16_rowmajor(Bt, "Bt")
         self.heap = heap
@@ -96,6 +96,7 @@ class GemmRs:
         d.timeout_ns = int(timeout_ms * 1e6)
         d.group_m, d.num_ctas = group_m, num_ctas
         d.ablate = ablate
+        d.rs_signal_batch = signal_batch      # finished tiles per system-scope fence of the signalling warp (0 = default)
         d.epi_st256 = 1 if st256 else 0    # 32-byte epilogue stores (st.global.v8.b32) instead of 16-byte ones
         # hold_operands=False: the caller re-points the plan with plan.set_operands() and owns the operands' lifetime
         own = (self.stage, self.tile_cnt, self.barrier, self.out)
