@@ -44,6 +44,11 @@ def parse_args():
     ap.add_argument("--n-ag", type=int, default=28672, help="global N of the AG+GEMM, sharded over the GPUs")
     ap.add_argument("--gather-rows", type=int, default=512)
     ap.add_argument("--cta-group", type=int, default=2)
+    ap.add_argument("--rs-cta-group", type=int, default=0, help="CTA form of the GEMM+RS alone (0 = --cta-group)")
+    ap.add_argument("--signal-batch", type=int, default=0, help="GEMM+RS: finished tiles per system-scope fence (0 = library default)")
+    ap.add_argument("--gather-warps", type=int, default=0, help="AG+GEMM: gather warps per CTA (0 = library default)")
+    ap.add_argument("--ag-group-m", type=int, default=0, help="AG+GEMM: raster group height (0 = library default)")
+    ap.add_argument("--ag-vec32", type=int, default=-1, help="AG+GEMM: 32-byte gather moves, 0 or 1 (-1 = library default)")
     ap.add_argument("--pre-barrier", type=int, default=1, help="1: a device barrier over all ranks runs (untimed) ahead of every timed operation; "
                                                                 "0: operations follow each other directly and rank skew is charged to the next one")
     ap.add_argument("--no-baseline", action="store_true")
@@ -99,8 +104,12 @@ def main():
     ew.fill_normal_(A_rs, seed=10 + rank)
     ew.fill_normal_(Bt_rs, seed=110 + rank)
     ew.fill_normal_(Bt_ag, seed=210 + rank, std=0.02)
-    rs = GemmRs(heap, A_rs, Bt_rs, cta_group=args.cta_group)
-    ag = AgGemm(heap, M, K_ag, Bt_ag, cta_group=args.cta_group, gather_rows=args.gather_rows)
+    rs_kw = dict(cta_group=args.rs_cta_group or args.cta_group, signal_batch=args.signal_batch)
+    ag_kw = dict(cta_group=args.cta_group, gather_rows=args.gather_rows, gather_warps=args.gather_warps, group_m=args.ag_group_m)
+    if args.ag_vec32 >= 0:
+        ag_kw["vec32"] = bool(args.ag_vec32)
+    rs = GemmRs(heap, A_rs, Bt_rs, **rs_kw)
+    ag = AgGemm(heap, M, K_ag, Bt_ag, **ag_kw)
     ew.fill_normal_(ag.a_shard, seed=310 + rank)
     torch.cuda.synchronize()
     G.host_barrier()
@@ -263,8 +272,8 @@ def main():
         a_host.copy_(A_rs)
         x_host.copy_(ag.a_shard)
         A_rs2 = torch.empty_like(A_rs)
-        rs2 = GemmRs(heap, A_rs2, Bt_rs, cta_group=args.cta_group)
-        ag2 = AgGemm(heap, M, K_ag, Bt_ag, cta_group=args.cta_group, gather_rows=args.gather_rows, out=ag.out)
+        rs2 = GemmRs(heap, A_rs2, Bt_rs, **rs_kw)
+        ag2 = AgGemm(heap, M, K_ag, Bt_ag, out=ag.out, **ag_kw)
         sets = [(A_rs, rs, ag), (A_rs2, rs2, ag2)]
         copy_stream = torch.cuda.Stream()
         ready = [torch.cuda.Event() for _ in sets]       # inputs of the set have landed
@@ -334,7 +343,7 @@ def main():
             "config": {"model": "flux-style TP GEMM pair (Llama-3-70B MLP shapes)",
                        "gemm_rs": {"M": M, "N": N_rs, "K_global": args.k_rs, "K_per_rank": K_rs},
                        "ag_gemm": {"M": M, "K": K_ag, "N_global": args.n_ag, "N_per_rank": N_ag, "gather_rows": args.gather_rows},
-                       "global_batch": M, "seq_len": None, "parallelism": f"tp{tp}", "cta_group": args.cta_group,
+                       "global_batch": M, "seq_len": None, "parallelism": f"tp{tp}", "cta_group": args.cta_group, "knobs": {"gemm_rs": rs_kw, "ag_gemm": {k: v for k, v in ag_kw.items() if k != "gather_rows"}},
                        "l2": "flushed ahead of every timed operation (256 MiB write); inputs also exceed L2",
                        "timing": ("fused and NCCL+cuBLAS steps alternate inside one timed loop and take turns at going first; a step is the sum of its two operations, each timed by "
                                   "its own pair of CUDA events" + (", behind an untimed device barrier over all ranks" if args.pre_barrier else ""))},
@@ -353,7 +362,7 @@ def main():
             "pct_roofline": round(100.0 * roof_us / step_us, 1),
             "pct_roofline_gemm_rs": f_rs["pct"], "pct_roofline_ag_gemm": f_ag["pct"],
             "pct_roofline_detail": {"gemm_rs": f_rs, "ag_gemm": f_ag},
-            "wave_efficiency": {"gemm_rs": round(roofline.wave_efficiency(M, N_rs, args.cta_group)["efficiency"], 4),
+            "wave_efficiency": {"gemm_rs": round(roofline.wave_efficiency(M, N_rs, rs_kw["cta_group"])["efficiency"], 4),
                                 "ag_gemm": round(roofline.wave_efficiency(M, N_ag, args.cta_group)["efficiency"], 4),
                                 "note": "share of the persistent grid's tile slots that hold a tile; not folded into the roofline"},
             "verified": verified, "verify_errors": errs,

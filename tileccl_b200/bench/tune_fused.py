@@ -135,11 +135,13 @@ def main(argv=None) -> int:
         K = args.k if args.k > 0 else args.k_global // world
         names = [n for n in RS_SETTINGS if only is None or n in only]
         mc_ok = world > 1 and bool(_native.lib().tcl_multicast_supported(torch.cuda.current_device()))
-        if not mc_ok and "nvls" in names:
-            names.remove("nvls")
         per_plan = M * N * 2 + (M // world) * N * 2 + (1 << 20)
-        heap = SymmetricHeap(len(names) * per_plan + (64 << 20))
-        mc_heap = SymmetricHeap(per_plan + (64 << 20), backend="vmm", multicast=True) if "nvls" in names else None
+        n_nvls = sum(1 for n in names if RS_SETTINGS[n].get("transport") == "nvls")
+        if not mc_ok:
+            names = [n for n in names if RS_SETTINGS[n].get("transport") != "nvls"]
+            n_nvls = 0
+        heap = SymmetricHeap((len(names) - n_nvls) * per_plan + (64 << 20))
+        mc_heap = SymmetricHeap(n_nvls * per_plan + (64 << 20), backend="vmm", multicast=True) if n_nvls else None
         try:
             A = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
             Bt = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
