@@ -86,3 +86,18 @@ def test_wave_efficiency_of_the_persistent_grid():
     assert (w["tiles"], w["groups"], w["waves"]) == (4096, 74, 56) and abs(w["efficiency"] - 4096 / (56 * 74)) < 1e-12
     assert roofline.wave_efficiency(256 * 74, 256)["efficiency"] == 1.0     # exactly one full wave
     assert roofline.wave_efficiency(128, 256, cta_group=1)["efficiency"] == 1 / 148
+
+
+def test_turn_order_changes_every_variants_predecessor():
+    from collections import Counter
+    from tileccl_b200.bench._common import turn_order
+    names = [f"v{i}" for i in range(12)]
+    pred = Counter()
+    for i in range(24):
+        order = turn_order(names, i)
+        assert sorted(order) == sorted(names)
+        for a, b in zip(order, order[1:]):
+            pred[(a, b)] += 1
+    # no variant follows the same neighbour in more than a third of the iterations
+    assert max(pred.values()) <= 8
+    assert turn_order(["a", "b"], 1) == ["b", "a"] and turn_order([], 3) == []

@@ -61,6 +61,21 @@ def timed_series(fn, iters: int, warmup: int, before=None, flush=None) -> list[f
     return [a.elapsed_time(b) * 1e3 for a, b in zip(s, e)]
 
 
+def turn_order(names: list, i: int) -> list:
+    """The order of the variants in iteration ``i``: a different start and a different stride every iteration
+    (strides coprime to the count), so that over a run no variant keeps the same predecessor.  A plain rotation
+    would change who goes first but leave every variant behind the same neighbour, and a kernel that always
+    follows the power-hungry library GEMM always starts at a lower clock.  Deterministic: every rank gets the
+    same order."""
+    n = len(names)
+    if n < 3:
+        return names[i % n:] + names[:i % n] if n else []
+    import math
+    strides = [s for s in range(1, n) if math.gcd(s, n) == 1]
+    s = strides[i % len(strides)]
+    return [names[(i + j * s) % n] for j in range(n)]
+
+
 def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=None, rotate: bool = True) -> dict:
     """Like :func:`timed_series` for several variants at once, taking one
     iteration of each in turn, so that all of them see the same clocks and
@@ -68,7 +83,7 @@ def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=Non
     comm_comp/exp1_ce_interference.cu:545-548).  With ``rotate`` the turn starts
     one variant later every iteration, so that no variant always runs right
     after the same neighbour (a kernel that follows a power-hungry one starts at
-    a lower clock); every rank rotates alike."""
+    a lower clock, see :func:`turn_order`); every rank orders alike."""
     names = list(fns)
     for _ in range(warmup):
         for n in names:
@@ -80,8 +95,7 @@ def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=Non
     ev = {n: ([torch.cuda.Event(enable_timing=True) for _ in range(iters)],
               [torch.cuda.Event(enable_timing=True) for _ in range(iters)]) for n in names}
     for i in range(iters):
-        k = i % len(names) if rotate else 0
-        for n in names[k:] + names[:k]:
+        for n in turn_order(names, i) if rotate else names:
             if flush:
                 flush()
             if before:
