@@ -173,7 +173,7 @@ def plan(n_gpus: int, quick: bool, out: Path, tuning: bool = False, iters: int =
             steps.append((f"exp3_order_{order.split(',')[0]}", launch + ["exp3_gemm_rs_fused", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it,
                                                                         "--order", order, "--csv", f"{o}/exp3_order.csv"], 600, 2))
     steps.append(("exp3_epilogue", launch + ["exp3_epilogue_remote", "--sizes", "8192,32768x8192x1024" if quick else "8192,8192x8192x512,512x8192x8192,32768x8192x8192,32768x8192x1024",
-                                             "--iters", it, "--verify", "--csv", f"{o}/exp3_epilogue.csv"], 900, 2))
+                                             "--iters", it, "--verify", "--csv", f"{o}/exp3_epilogue.csv"] + ([] if quick else ["--epi", "st16,st256,tma"]), 900, 2))
     steps.append(("exp2_ag_gemm", launch + ["exp2_ag_gemm_granularity", "--m", "32768", "--k", "8192", "--n-global", "28672", "--gather-rows", "512,4096" if quick else "128,512,2048,4096",
                                             "--iters", it2, "--verify", "--csv", f"{o}/exp2.csv"], 1200, 2))
     steps.append(("nvls_bw", launch + ["nvls_bw", "--csv", f"{o}/nvls_bw.csv"] + (["--sizes", "64K,16M,256M", "--iters", "10"] if quick else []), 600, 2))
