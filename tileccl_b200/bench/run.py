@@ -50,6 +50,40 @@ def split_batch(argv: list[str]) -> tuple[dict, list[tuple[str, str, list[str]]]
     return opts, jobs
 
 
+class StallDump:
+    """With TILECCL_STALL_DUMP_S=<seconds> set, an experiment that is still running after that long gets the
+    Python stack of every thread of every rank written to ``stall.<experiment>.rank<r>.txt`` (in
+    TILECCL_STALL_DUMP_DIR, default: the log directory or the working directory), again every <seconds>: where
+    each rank sits when a collective never completes.  Nothing is written, and the file is removed, when the
+    experiment ends in time."""
+
+    def __init__(self, name: str, where: str | None):
+        self.file = None
+        try:
+            self.seconds = float(os.environ.get("TILECCL_STALL_DUMP_S", "0") or 0)
+        except ValueError:
+            self.seconds = 0.0
+        if self.seconds > 0:
+            d = os.environ.get("TILECCL_STALL_DUMP_DIR") or where or "."
+            self.path = os.path.join(d, f"stall.{name}.rank{os.environ.get('RANK', '0')}.txt")
+
+    def __enter__(self):
+        if self.seconds > 0:
+            import faulthandler
+            self.file = open(self.path, "w")
+            faulthandler.dump_traceback_later(self.seconds, repeat=True, file=self.file)
+        return self
+
+    def __exit__(self, *exc):
+        if self.file is not None:
+            import faulthandler
+            faulthandler.cancel_dump_traceback_later()
+            self.file.close()
+            if os.path.getsize(self.path) == 0:
+                os.remove(self.path)
+        return False
+
+
 def main() -> int:
     opts, jobs = split_batch(sys.argv[1:])
     if not jobs or any(mod not in EXPERIMENTS for _, mod, _ in jobs):
@@ -57,7 +91,8 @@ def main() -> int:
         return 1
     if len(jobs) == 1 and not opts["manifest"] and not opts["logs"]:
         mod = importlib.import_module(f"tileccl_b200.bench.{jobs[0][1]}")
-        return int(mod.main(jobs[0][2]) or 0)
+        with StallDump(jobs[0][0], None):
+            return int(mod.main(jobs[0][2]) or 0)
 
     import torch
     from tileccl_b200.parallel import group as G
@@ -67,10 +102,11 @@ def main() -> int:
     try:
         for name, modname, flags in jobs:
             t0 = time.time()
-            log = open(os.path.join(opts["logs"], f"{name}.log"), "w") if (opts["logs"] and rank == 0) else None
+            log = open(os.path.join(opts["logs"], f"{name}.log"), "w", buffering=1) if (opts["logs"] and rank == 0) else None
             rc = 0
             try:
                 with contextlib.ExitStack() as st:
+                    st.enter_context(StallDump(name, opts["logs"]))
                     if log:
                         log.write(f"$ {modname} {' '.join(flags)}\n")
                         log.flush()

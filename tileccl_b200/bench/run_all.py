@@ -101,6 +101,35 @@ class Sampler:
                 self.proc.kill()
 
 
+_running: dict = {"proc": None}      # the step in flight, for the signal handler
+
+
+def end_group(p, grace: float = 30.0) -> None:
+    """Ends a step's whole process group (the launcher and every rank): SIGINT first, SIGKILL after ``grace``."""
+    try:
+        os.killpg(p.pid, signal.SIGINT)
+    except ProcessLookupError:
+        return
+    try:
+        p.wait(timeout=grace)
+    except subprocess.TimeoutExpired:
+        os.killpg(p.pid, signal.SIGKILL)
+        p.wait()
+
+
+def install_signal_handlers(log) -> None:
+    """A step runs in a session of its own, so a signal that ends the orchestrator would leave its ranks behind,
+    still holding the GPUs.  SIGTERM / SIGINT / SIGHUP therefore end the running step's process group first."""
+    def handler(signum, _frame):
+        p = _running["proc"]
+        log(f"signal {signum}: ending the running step and leaving")
+        if p is not None and p.poll() is None:
+            end_group(p, grace=10.0)
+        raise SystemExit(128 + signum)
+    for sig in (signal.SIGTERM, signal.SIGINT, signal.SIGHUP):
+        signal.signal(sig, handler)
+
+
 def run_step(name: str, cmd: list[str], timeout: float, out: Path, log, manifest: bool = True) -> int:
     """Runs one experiment in its own process group; on time-out the group (and only it) is killed.
     ``manifest=False``: the command writes the manifest lines of its parts itself (a batched launch)."""
@@ -109,16 +138,14 @@ def run_step(name: str, cmd: list[str], timeout: float, out: Path, log, manifest
         lf.write("$ " + " ".join(cmd) + "\n")
         lf.flush()
         p = subprocess.Popen(cmd, stdout=lf, stderr=subprocess.STDOUT, cwd=str(PKG.parent), start_new_session=True)
+        _running["proc"] = p
         try:
             rc = p.wait(timeout=timeout)
         except subprocess.TimeoutExpired:
-            os.killpg(p.pid, signal.SIGINT)
-            try:
-                p.wait(timeout=30)
-            except subprocess.TimeoutExpired:
-                os.killpg(p.pid, signal.SIGKILL)
-                p.wait()
+            end_group(p)
             rc = 124
+        finally:
+            _running["proc"] = None
     dur = time.time() - t0
     if manifest or rc != 0:
         with open(out / "manifest.txt", "a") as mf:
@@ -179,11 +206,12 @@ def plan(n_gpus: int, quick: bool, out: Path, tuning: bool = False, iters: int =
     steps.append(("nvls_bw", launch + ["nvls_bw", "--csv", f"{o}/nvls_bw.csv"] + (["--sizes", "64K,16M,256M", "--iters", "10"] if quick else []), 600, 2))
     steps.append(("exp3_fused_nvls", launch + ["exp3_gemm_rs_fused", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it, "--transport", "nvls", "--verify",
                                                 "--csv", f"{o}/exp3_fused_nvls.csv"], 600, 2))
-    if tuning:
-        # knob sweeps of both fused ops at the headline shapes: all settings in one process per rank, timed in turn
-        steps.append(("tune_fused", launch + ["tune_fused", "--ops", "rs,ag", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it2,
-                                              "--csv", f"{o}/exp3_tuning.csv"], 900, 2))
     steps.append(("mlp_e2e", launch + ["mlp_e2e", "--iters", it2 if iters > 0 or quick else "50", "--verify", "--csv", f"{o}/mlp_e2e.csv"], 900, 1))
+    if tuning:
+        # knob sweeps of both fused ops at the headline shapes: all settings in one process per rank, timed in turn.
+        # Dozens of plans live side by side in it, so it runs as a launch of its own (a plain list is never batched).
+        steps.append(("tune_fused", list(launch + ["tune_fused", "--ops", "rs,ag", "--m", "32768", "--n", "8192", "--k-global", "8192", "--iters", it2,
+                                                   "--csv", f"{o}/exp3_tuning.csv"]), 150, 2))
     steps.append(("bench", [py, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={max(1, n_gpus)}", "--master-addr", "127.0.0.1", "--master-port", "29571",
                             "bench.py", "--gpus", str(max(1, n_gpus)), "--steps", it2, "--warmup", "5"], 900, 1))
     # ---- C++ programs (single process, several GPUs) ----
@@ -232,7 +260,9 @@ def batch_rank_steps(steps, out: Path):
             tail = ["--manifest", str(out / "manifest.txt"), "--logs", str(out)]
             for i, (name, cmd, _to, _need) in enumerate(run):
                 tail += (["--then"] if i else []) + cmd.tail + ["--as", name]
-            merged.append((f"batch_{run[0][0]}..{run[-1][0]}", prefix + tail, sum(t for _, _, t, _ in run), max(n for _, _, _, n in run)))
+            # the parts' own limits are generous; a whole batch gets at most a quarter of their sum (and at least ten minutes)
+            limit = max(600.0, 0.25 * sum(t for _, _, t, _ in run))
+            merged.append((f"batch_{run[0][0]}..{run[-1][0]}", prefix + tail, limit, max(n for _, _, _, n in run)))
         run.clear()
 
     for st in steps:
@@ -316,6 +346,7 @@ def main(argv=None) -> int:
             f.write(line + "\n")
 
     log(f"bundle {out}  gpus={n} quick={args.quick} resume={bool(args.resume)}")
+    install_signal_handlers(log)
     env_snapshot(out)
     if n and not precheck(log, args.force):
         return 2
