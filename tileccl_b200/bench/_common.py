@@ -76,14 +76,19 @@ def turn_order(names: list, i: int) -> list:
     return [names[(i + j * s) % n] for j in range(n)]
 
 
-def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=None, rotate: bool = True) -> dict:
+def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=None, rotate: bool = True, check=None) -> dict:
     """Like :func:`timed_series` for several variants at once, taking one
     iteration of each in turn, so that all of them see the same clocks and
     temperature (the paired-baseline discipline of the reference,
     comm_comp/exp1_ce_interference.cu:545-548).  With ``rotate`` the turn starts
     one variant later every iteration, so that no variant always runs right
     after the same neighbour (a kernel that follows a power-hungry one starts at
-    a lower clock, see :func:`turn_order`); every rank orders alike."""
+    a lower clock, see :func:`turn_order`); every rank orders alike.
+
+    ``check`` (optional) is called on every rank after the warm-up and should raise if a variant
+    reported a failure (a bounded wait that ran out).  The ranks then agree on the outcome and all of
+    them raise, naming rank and variant, before the timed loop starts: a variant whose every launch
+    sits out its time-out would otherwise hold the GPUs for iterations x time-out."""
     names = list(fns)
     for _ in range(warmup):
         for n in names:
@@ -91,6 +96,15 @@ def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=Non
                 before()
             fns[n]()
     torch.cuda.synchronize()
+    if check is not None:
+        err = None
+        try:
+            check()
+        except Exception as e:  # noqa: BLE001  (reported on every rank below)
+            err = f"{type(e).__name__}: {e}"
+        errs = G.all_gather_object(err)
+        if any(errs):
+            raise RuntimeError("failed during warm-up: " + "; ".join(f"rank {r}: {e}" for r, e in enumerate(errs) if e))
     G.host_barrier()
     ev = {n: ([torch.cuda.Event(enable_timing=True) for _ in range(iters)],
               [torch.cuda.Event(enable_timing=True) for _ in range(iters)]) for n in names}

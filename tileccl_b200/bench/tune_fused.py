@@ -81,7 +81,15 @@ def _sweep(op, names, settings, build, baseline, heap, args, roof, dims, base_kn
     runners = {n: plans[n] for n in common}
     runners["nccl"] = baseline
     bar = ew.DeviceBarrier(heap)
-    series = C.timed_interleaved(runners, args.iters, args.warmup, before=bar, flush=L2Flusher())
+    def check_all():
+        bar.check()
+        for n in common:
+            try:
+                plans[n].check()
+            except Exception as e:  # noqa: BLE001
+                raise RuntimeError(f"setting {n}: {type(e).__name__}: {e}") from e
+
+    series = C.timed_interleaved(runners, args.iters, args.warmup, before=bar, flush=L2Flusher(), check=check_all)
     torch.cuda.synchronize()
     bar.check()
     for n in common:
