@@ -34,7 +34,7 @@ __global__ void pingpong_kernel(int* my_flag, int* peer_flag, int rounds, int ro
   unsigned long long t0 = 0;
   for (int r = 1; r <= rounds; ++r) {
     if (role == 0) {
-      if (r == 2) t0 = globaltimer_ns();  // round 1 absorbs the launch skew
+      if (r == 2) t0 = globaltimer_ns();  // the first round trip absorbs the launch skew
       st_release_sys(peer_flag, r);
       if (!spin_until(my_flag, r, deadline)) { *err = 1; return; }
     } else {
