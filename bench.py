@@ -367,6 +367,7 @@ def main():
                                 "note": "share of the persistent grid's tile slots that hold a tile; not folded into the roofline"},
             "verified": verified, "verify_errors": errs,
             "clocks": clocks, "e2e": e2e, "gpu_launches": gpu_launches, "impl": "tileccl_b200",
+            "host_numa": G.numa_info,
         }
         if not verified:
             # A wrong result is not a measurement: no value, and a failing exit code.

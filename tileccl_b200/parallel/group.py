@@ -15,6 +15,9 @@ import torch
 import torch.distributed as dist
 
 
+numa_info: dict = {}       # what :func:`init` found and did about CPU affinity (utils/numa.py)
+
+
 def env_rank_world() -> tuple[int, int, int]:
     """(rank, world, local_rank) from the launcher's environment (1 process if unset)."""
     rank = int(os.environ.get("RANK", "0"))
@@ -33,6 +36,10 @@ def init(backend: str | None = None, timeout_s: float = 600.0) -> tuple[int, int
     use_cuda = torch.cuda.is_available()
     if use_cuda:
         torch.cuda.set_device(local % max(1, torch.cuda.device_count()))
+        # host buffers this rank pins from here on land on its GPU's NUMA node (no-op where unknown)
+        global numa_info
+        from ..utils.numa import bind_to_gpu_node
+        numa_info = bind_to_gpu_node(torch.cuda.current_device())
     if world > 1 and not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29511")
