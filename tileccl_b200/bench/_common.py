@@ -76,6 +76,20 @@ def turn_order(names: list, i: int) -> list:
     return [names[(i + j * s) % n] for j in range(n)]
 
 
+def agree_no_failure(check, what: str = "step") -> None:
+    """Runs ``check()`` on this rank, then lets all ranks agree: if it raised anywhere, every rank raises the
+    same RuntimeError naming the ranks and their messages.  A failure seen by one rank only would otherwise
+    leave the others waiting for it in their next collective."""
+    err = None
+    try:
+        check()
+    except Exception as e:  # noqa: BLE001  (reported on every rank below)
+        err = f"{type(e).__name__}: {e}"
+    errs = G.all_gather_object(err)
+    if any(errs):
+        raise RuntimeError(f"failed during {what}: " + "; ".join(f"rank {r}: {e}" for r, e in enumerate(errs) if e))
+
+
 def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=None, rotate: bool = True, check=None) -> dict:
     """Like :func:`timed_series` for several variants at once, taking one
     iteration of each in turn, so that all of them see the same clocks and
@@ -97,14 +111,7 @@ def timed_interleaved(fns: dict, iters: int, warmup: int, before=None, flush=Non
             fns[n]()
     torch.cuda.synchronize()
     if check is not None:
-        err = None
-        try:
-            check()
-        except Exception as e:  # noqa: BLE001  (reported on every rank below)
-            err = f"{type(e).__name__}: {e}"
-        errs = G.all_gather_object(err)
-        if any(errs):
-            raise RuntimeError("failed during warm-up: " + "; ".join(f"rank {r}: {e}" for r, e in enumerate(errs) if e))
+        agree_no_failure(check, "warm-up")
     G.host_barrier()
     ev = {n: ([torch.cuda.Event(enable_timing=True) for _ in range(iters)],
               [torch.cuda.Event(enable_timing=True) for _ in range(iters)]) for n in names}
