@@ -113,7 +113,13 @@ def main(argv=None) -> int:
     dev = torch.device("cuda", torch.cuda.current_device())
     modes = C.split_csv(args.modes)
     grains = [min(int(g), seg) for g in C.split_csv(args.gather_rows)]
+    asked = sorted(set(grains))
     grains = sorted(set(g for g in grains if seg % g == 0 and g % (128 * args.cta_group) == 0 or g == seg))
+    if rank == 0:
+        for g in asked:
+            if g not in grains:
+                print(f"# gather tile {g} rows skipped: it must divide the {seg}-row segment and be a multiple of the "
+                      f"{128 * args.cta_group}-row tile (--cta-group 1 allows 128)")
     heap = SymmetricHeap((3 * len(grains) + 1) * (M * K * 2 + (8 << 20)) + (64 << 20))
     Bt = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
     ew.fill_normal_(Bt, seed=500 + rank, std=0.02)
