@@ -68,6 +68,8 @@ class CePipeline:
         seg = M // world
         self.chunk_rows = chunk_rows
         self.comm = torch.cuda.Stream(priority=-1)
+        if chunk_rows % (128 * cta_group) != 0:
+            cta_group = 1        # a 128-row chunk is one single-CTA tile high
         self.chunks = []     # (row0, src_ptr, dst_ptr, bytes, src_dev, event, plan)
         order = [(rank + s) % world for s in range(world)]
         for s in order:
@@ -114,12 +116,12 @@ def main(argv=None) -> int:
     modes = C.split_csv(args.modes)
     grains = [min(int(g), seg) for g in C.split_csv(args.gather_rows)]
     asked = sorted(set(grains))
-    grains = sorted(set(g for g in grains if seg % g == 0 and g % (128 * args.cta_group) == 0 or g == seg))
+    # A CTA's TMA producer waits for the 128 rows it loads itself, also in a CTA pair: 128 is the finest tile.
+    grains = sorted(set(g for g in grains if seg % g == 0 and g % 128 == 0 or g == seg))
     if rank == 0:
         for g in asked:
             if g not in grains:
-                print(f"# gather tile {g} rows skipped: it must divide the {seg}-row segment and be a multiple of the "
-                      f"{128 * args.cta_group}-row tile (--cta-group 1 allows 128)")
+                print(f"# gather tile {g} rows skipped: it must divide the {seg}-row segment and be a multiple of 128")
     heap = SymmetricHeap((3 * len(grains) + 1) * (M * K * 2 + (8 << 20)) + (64 << 20))
     Bt = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
     ew.fill_normal_(Bt, seed=500 + rank, std=0.02)
