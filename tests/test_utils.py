@@ -101,3 +101,11 @@ def test_turn_order_changes_every_variants_predecessor():
     # no variant follows the same neighbour in more than a third of the iterations
     assert max(pred.values()) <= 8
     assert turn_order(["a", "b"], 1) == ["b", "a"] and turn_order([], 3) == []
+
+
+def test_gather_tiles_of_the_ag_gemm_sweep():
+    from tileccl_b200.bench.exp2_ag_gemm_granularity import gather_tiles
+    assert gather_tiles(["128", "512", "2048", "4096"], 4096) == ([128, 512, 2048, 4096], [])      # 8 ranks
+    assert gather_tiles(["128", "512", "2048", "4096"], 16384) == ([128, 512, 2048, 4096], [])     # 2 ranks
+    assert gather_tiles(["64", "384", "8192"], 4096) == ([4096], [64, 384])                         # 8192 becomes the segment
+    assert gather_tiles(["192"], 192) == ([192], [])                                                # the whole segment always runs

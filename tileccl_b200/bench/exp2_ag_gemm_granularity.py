@@ -57,6 +57,15 @@ def build_parser():
     return ap
 
 
+def gather_tiles(asked, seg: int) -> tuple[list[int], list[int]]:
+    """(tiles to run, tiles skipped) for a segment of ``seg`` rows.  A tile larger than the segment becomes the
+    segment.  A CTA's TMA producer waits for the 128 rows it loads itself, also in a CTA pair, so 128 rows is the
+    finest tile; a tile must divide the segment."""
+    want = sorted(set(min(int(g), seg) for g in asked))
+    run = [g for g in want if g == seg or (seg % g == 0 and g % 128 == 0)]
+    return run, [g for g in want if g not in run]
+
+
 class CePipeline:
     """Segmented launch + copy-engine transfers (the reference's exp2 design)."""
 
@@ -114,14 +123,10 @@ def main(argv=None) -> int:
     seg = M // world
     dev = torch.device("cuda", torch.cuda.current_device())
     modes = C.split_csv(args.modes)
-    grains = [min(int(g), seg) for g in C.split_csv(args.gather_rows)]
-    asked = sorted(set(grains))
-    # A CTA's TMA producer waits for the 128 rows it loads itself, also in a CTA pair: 128 is the finest tile.
-    grains = sorted(set(g for g in grains if seg % g == 0 and g % 128 == 0 or g == seg))
+    grains, skipped = gather_tiles(C.split_csv(args.gather_rows), seg)
     if rank == 0:
-        for g in asked:
-            if g not in grains:
-                print(f"# gather tile {g} rows skipped: it must divide the {seg}-row segment and be a multiple of 128")
+        for g in skipped:
+            print(f"# gather tile {g} rows skipped: it must divide the {seg}-row segment and be a multiple of 128")
     heap = SymmetricHeap((3 * len(grains) + 1) * (M * K * 2 + (8 << 20)) + (64 << 20))
     Bt = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
     ew.fill_normal_(Bt, seed=500 + rank, std=0.02)
